@@ -1,0 +1,108 @@
+// Host-side declarations shared by the kernel translation units and the manager.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+#include "../../include/uep_b200.h"
+#include "common.cuh"
+
+namespace uep {
+
+constexpr int kMaxLocalRanks = 8;  // ranks one manager can host on one device (simulated EP)
+constexpr int kMaxPeers = kMaxRanksPerDomain;
+
+// Device-resident, per hosted rank, immutable after connect. Peer tables are indexed
+// by global rank; entry [my_rank] is this rank's own buffer.
+struct RankDev {
+    int my_rank;
+    int num_ranks;
+    // plan exchange
+    int32_t* local_hist;     // [Lpad], zero between calls
+    int* plan_ticket;        // zero between calls
+    int32_t* peer_gather[kMaxPeers];  // each: [2][N][Lpad] int32
+    uint64_t* peer_gather_flags[kMaxPeers];  // each: [2][N]
+    int32_t* global_loads;   // [L]
+    int32_t* loads_per_rank; // [N][L] latest gathered matrix (contiguous copy)
+    // weight sync / grad reduce
+    int* sync_ticket;        // zero between calls
+    uint8_t* peer_replica_weight[kMaxPeers];
+    uint8_t* peer_replica_scale[kMaxPeers];
+    float* peer_replica_grad[kMaxPeers];
+    uint64_t* peer_sync_flags[kMaxPeers];  // each: [N], entry [src] = last epoch src finished sending to that rank
+    DeviceStatus* status;    // mapped pinned host memory
+};
+
+struct PlanPtrs {
+    int32_t *p2l, *l2p, *lcnts, *quota, *quota_prefix, *rank_quota_prefix;
+};
+
+struct ShardLayout {  // bytes of the four weight shards and their place inside a replica slot
+    int64_t bytes[4];        // fc1, fc2, fc1 scale, fc2 scale
+    int64_t slot_offset[4];  // offset inside the weight slot (0,1) / scale slot (2,3)
+    int64_t weight_slot_stride, scale_slot_stride;
+    int num_shards;          // 2 or 4
+};
+
+// ---- launchers (defined in the .cu files; every launch bumps the launch counter) ----
+void count_launch(int n = 1);
+
+struct PlanCall {
+    const RankDev* rank[kMaxLocalRanks];
+    const void* input[kMaxLocalRanks];
+    int T[kMaxLocalRanks];
+    PlanPtrs plan[kMaxLocalRanks];
+    int nlocal;
+    int input_kind;  // 0 bool map, 1 ids32, 2 ids64
+    int K_or_L;
+    int N, G, M, R, D;
+    uep_solver_params params;
+    uint64_t epoch;
+    uint64_t timeout_ns;
+    int ctas_per_rank;
+};
+cudaError_t launch_plan(const PlanCall& call, cudaStream_t stream);
+int plan_ctas_per_rank(int input_kind, int max_T, int K_or_L, int nlocal, int num_sms);
+
+struct SyncCall {
+    const RankDev* rank[kMaxLocalRanks];
+    PlanPtrs plan[kMaxLocalRanks];
+    const int64_t* src_ptrs[kMaxLocalRanks][4];  // device int64[M] tables; scale tables may be null
+    int nlocal;
+    int N, M, R, D;
+    ShardLayout shards;
+    uint64_t epoch;
+    uint64_t timeout_ns;
+    int ctas_per_rank;
+};
+cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream);
+int weight_sync_max_ctas_per_rank(int nlocal, int num_sms);
+
+struct ReduceCall {
+    const RankDev* rank[kMaxLocalRanks];
+    PlanPtrs plan[kMaxLocalRanks];
+    const int64_t* fc1_grad_ptrs[kMaxLocalRanks];
+    const int64_t* fc2_grad_ptrs[kMaxLocalRanks];
+    int nlocal;
+    int N, M, R, D;
+    int64_t fc1_numel, fc2_numel;
+    uint64_t timeout_ns;
+    int ctas_per_rank;
+};
+cudaError_t launch_grad_reduce(const ReduceCall& call, cudaStream_t stream);
+
+// stateless reroute / dispatch launchers are reached through the C ABI directly.
+
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+int fail_cuda(cudaError_t e, const char* what);
+
+}  // namespace uep
+
+#define UEP_CUDA_TRY(expr)                                         \
+    do {                                                           \
+        cudaError_t _e = (expr);                                   \
+        if (_e != cudaSuccess) return ::uep::fail_cuda(_e, #expr); \
+    } while (0)

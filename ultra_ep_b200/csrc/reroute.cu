@@ -1,0 +1,597 @@
+// Kernel 2 — reroute: logical expert ids -> physical replica ids under the rank's
+// quota split, in dense ([T,L] -> [T,P]) and sparse ([T,K]) form, the dense backward
+// gather, and the token-gradient row gather.
+//
+// The reference resolves the ordinal of a token inside its expert with one warp per
+// (expert, 128-token tile) reading the bool map column-wise, and writes the [T,P]
+// outputs twice (zero-fill, then scatter): csrc/kernels/reroute.cu:21-51, 138-264 and
+// csrc/ultra_ep.cpp:891-892 of the reference. Here:
+//   * pass 1 counts keys per (tile, expert) from coalesced row reads;
+//   * pass 2 turns the counts of the preceding tiles into a base per expert, resolves
+//     ordinals inside the tile in row-major order (deterministically: per-warp sub-counts,
+//     then match.any inside the warp), and writes every output element exactly once with
+//     coalesced vector stores (zeros included), so no pre-zeroing pass exists.
+// Results equal the reference's dense rule bit for bit; the sparse form applies the same
+// rule per (token, k) entry and therefore is deterministic, which the reference's
+// atomic-counter sparse kernel (reroute.cu:492-515) is not.
+
+#include "internal.h"
+
+namespace uep {
+
+namespace {
+
+constexpr int kRerouteThreads = 256;
+constexpr int kDenseTileRows = 64;
+constexpr int kSparseTileEntries = 2048;  // 8 warps x 256 entries
+
+__device__ __forceinline__ int gcd_int(int a, int b) {
+    while (b != 0) {
+        const int t = a % b;
+        a = b;
+        b = t;
+    }
+    return a;
+}
+
+// Per-expert routing parameters (csrc/kernels/reroute.cu:182-209 of the reference).
+struct Router {
+    int C, total, stride, offset;
+};
+
+__device__ __forceinline__ Router make_router(int e, const int32_t* lcnts, const int32_t* rqp, int D, bool quota_mode,
+                                              bool interleave) {
+    Router r;
+    r.C = lcnts[e];
+    r.total = 0;
+    r.stride = 1;
+    r.offset = 0;
+    if (quota_mode && r.C > 0) r.total = rqp[static_cast<int64_t>(e) * D + r.C - 1];
+    if (quota_mode && interleave && r.total > 1) {
+        int s = r.total / 2 + 1;
+        if (s >= r.total) s = r.total - 1;
+        if (s < 1) s = 1;
+        while (gcd_int(s, r.total) != 1) {
+            ++s;
+            if (s >= r.total) s = 1;
+        }
+        r.stride = s;
+        r.offset = e % r.total;
+    } else {
+        r.stride = 0;  // marks "no interleave"
+    }
+    return r;
+}
+
+// ordinal -> replica index (reroute.cu:239-254 of the reference; round-robin: :126)
+__device__ __forceinline__ int replica_index(const Router& r, int e, int ordinal, const int32_t* rqp, int D,
+                                             bool quota_mode) {
+    if (!quota_mode) return ordinal % r.C;
+    int qr = ordinal;
+    if (r.stride != 0) qr = static_cast<int>((static_cast<long long>(ordinal) * r.stride + r.offset) % r.total);
+    const int32_t* prefix = rqp + static_cast<int64_t>(e) * D;
+    int idx = 0;
+    for (int j = 0; j < r.C; ++j) idx += (qr >= prefix[j]) ? 1 : 0;
+    return min(idx, max(r.C - 1, 0));
+}
+
+// ----------------------------------------------------------------------------- dense
+__global__ void __launch_bounds__(kRerouteThreads) dense_count_kernel(const uint8_t* __restrict__ map, int T, int L,
+                                                                      int32_t* __restrict__ tile_counts) {
+    const int tile = blockIdx.x;
+    const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
+    for (int e = threadIdx.x; e < L; e += blockDim.x) {
+        int c = 0;
+        for (int t = r0; t < r1; ++t) c += map[static_cast<int64_t>(t) * L + e] ? 1 : 0;
+        tile_counts[static_cast<int64_t>(tile) * L + e] = c;
+    }
+}
+
+__global__ void __launch_bounds__(kRerouteThreads)
+dense_scatter_kernel(const uint8_t* __restrict__ map, const float* __restrict__ probs, const int32_t* __restrict__ l2p,
+                     const int32_t* __restrict__ lcnts, const int32_t* __restrict__ rqp,
+                     const int32_t* __restrict__ tile_counts, uint8_t* __restrict__ out_map,
+                     float* __restrict__ out_probs, int T, int L, int P, int D, int quota_mode, int interleave,
+                     int vec_ok) {
+    extern __shared__ __align__(128) char smem_raw[];
+    // layout: inv[P] int32 | choice[rows][L] uint8
+    int32_t* inv = reinterpret_cast<int32_t*>(smem_raw);
+    uint8_t* choice = reinterpret_cast<uint8_t*>(inv + P);
+
+    const int tile = blockIdx.x;
+    const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
+    const int rows = r1 - r0;
+
+    for (int p = threadIdx.x; p < P; p += blockDim.x) inv[p] = -1;
+    __syncthreads();
+    for (int e = threadIdx.x; e < L; e += blockDim.x) {
+        const int C = lcnts[e];
+        for (int j = 0; j < C; ++j) {
+            const int p = l2p[static_cast<int64_t>(e) * D + j];
+            if (p >= 0 && p < P) inv[p] = e;
+        }
+        // base ordinal of this tile
+        int base = 0;
+        for (int tl = 0; tl < tile; ++tl) base += tile_counts[static_cast<int64_t>(tl) * L + e];
+        const Router router = make_router(e, lcnts, rqp, D, quota_mode != 0, interleave != 0);
+        int ordinal = base;
+        for (int t = 0; t < rows; ++t) {
+            uint8_t c = 0xFF;
+            if (map[static_cast<int64_t>(r0 + t) * L + e]) {
+                c = static_cast<uint8_t>(replica_index(router, e, ordinal, rqp, D, quota_mode != 0));
+                ++ordinal;
+            }
+            choice[t * L + e] = c;
+        }
+    }
+    __syncthreads();
+    // every output element of the tile, once
+    if (vec_ok) {
+        const int quads = P / 4;
+        for (int idx = threadIdx.x; idx < rows * quads; idx += blockDim.x) {
+            const int t = idx / quads, p0 = (idx % quads) * 4;
+            float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);
+            uint32_t mv = 0;
+            float* pvf = reinterpret_cast<float*>(&pv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int e = inv[p0 + k];
+                if (e >= 0) {
+                    const uint8_t c = choice[t * L + e];
+                    if (c != 0xFF && l2p[static_cast<int64_t>(e) * D + c] == p0 + k) {
+                        pvf[k] = probs[static_cast<int64_t>(r0 + t) * L + e];
+                        mv |= 1u << (8 * k);
+                    }
+                }
+            }
+            const int64_t o = static_cast<int64_t>(r0 + t) * P + p0;
+            *reinterpret_cast<float4*>(out_probs + o) = pv;
+            *reinterpret_cast<uint32_t*>(out_map + o) = mv;
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < rows * P; idx += blockDim.x) {
+            const int t = idx / P, p = idx % P;
+            float v = 0.f;
+            uint8_t m = 0;
+            const int e = inv[p];
+            if (e >= 0) {
+                const uint8_t c = choice[t * L + e];
+                if (c != 0xFF && l2p[static_cast<int64_t>(e) * D + c] == p) {
+                    v = probs[static_cast<int64_t>(r0 + t) * L + e];
+                    m = 1;
+                }
+            }
+            out_probs[static_cast<int64_t>(r0 + t) * P + p] = v;
+            out_map[static_cast<int64_t>(r0 + t) * P + p] = m;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kRerouteThreads)
+dense_backward_kernel(const float* __restrict__ grad_expanded, const uint8_t* __restrict__ map,
+                      const uint8_t* __restrict__ expanded_map, const int32_t* __restrict__ l2p,
+                      const int32_t* __restrict__ lcnts, float* __restrict__ grad_probs, int64_t total, int L, int P,
+                      int D) {
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        float g = 0.f;
+        if (map[idx]) {
+            const int64_t t = idx / L;
+            const int l = static_cast<int>(idx % L);
+            const int C = lcnts[l];
+            for (int r = 0; r < C; ++r) {
+                const int phys = l2p[static_cast<int64_t>(l) * D + r];
+                if (expanded_map[t * P + phys]) {
+                    g = grad_expanded[t * P + phys];
+                    break;
+                }
+            }
+        }
+        grad_probs[idx] = g;
+    }
+}
+
+// ---------------------------------------------------------------------------- sparse
+// bucket of a key: itself when in [0,nb_valid), else the last bucket (if there is one) or none
+template <typename IdT>
+__device__ __forceinline__ int key_bucket(IdT key, int nb_valid, bool tail_bucket) {
+    if (key >= 0 && key < nb_valid) return static_cast<int>(key);
+    return tail_bucket ? nb_valid : -1;
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kRerouteThreads) key_count_kernel(const IdT* __restrict__ keys, int64_t n,
+                                                                    int nb_valid, int tail_bucket,
+                                                                    int32_t* __restrict__ tile_counts) {
+    extern __shared__ __align__(128) char smem_raw[];
+    int32_t* hist = reinterpret_cast<int32_t*>(smem_raw);
+    const int nb = nb_valid + (tail_bucket ? 1 : 0);
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const int64_t begin = static_cast<int64_t>(blockIdx.x) * kSparseTileEntries;
+    const int64_t end = min(begin + kSparseTileEntries, n);
+    for (int64_t i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const int b = key_bucket<IdT>(keys[i], nb_valid, tail_bucket != 0);
+        if (b >= 0) atomicAdd(hist + b, 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) tile_counts[static_cast<int64_t>(blockIdx.x) * nb + i] = hist[i];
+}
+
+// Row-major ordinal of every entry of this CTA's tile inside its bucket. On return
+// `warp_base[w][b]` has been consumed; ordinals are handed to `emit(i, bucket, ordinal)`.
+// warp_base must hold (blockDim/32) * nb ints and already contain, for warp 0, nothing:
+// the function fills it. base[b] = number of entries of bucket b before this tile.
+template <typename IdT, typename Emit>
+__device__ void tile_ordinals(const IdT* keys, int64_t n, int nb_valid, bool tail_bucket,
+                              const int32_t* base, int32_t* warp_base, Emit emit) {
+    const int nb = nb_valid + (tail_bucket ? 1 : 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int per_warp = kSparseTileEntries / nwarps;
+    const int64_t tile_begin = static_cast<int64_t>(blockIdx.x) * kSparseTileEntries;
+    const int64_t wbegin = min(tile_begin + static_cast<int64_t>(warp) * per_warp, n);
+    const int64_t wend = min(wbegin + per_warp, n);
+
+    for (int i = threadIdx.x; i < nwarps * nb; i += blockDim.x) warp_base[i] = 0;
+    __syncthreads();
+    // A: per-warp counts
+    for (int64_t i = wbegin + lane; i < wend; i += kWarp) {
+        const int b = key_bucket<IdT>(keys[i], nb_valid, tail_bucket);
+        if (b >= 0) atomicAdd(warp_base + warp * nb + b, 1);
+    }
+    __syncthreads();
+    // B: exclusive scan over warps, seeded with the tile base
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+        int run = base[b];
+        for (int w = 0; w < nwarps; ++w) {
+            const int c = warp_base[w * nb + b];
+            warp_base[w * nb + b] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    // C: in-order resolution inside the warp
+    int32_t* mine = warp_base + warp * nb;
+    for (int64_t i0 = wbegin; i0 < wend; i0 += kWarp) {
+        const int64_t i = i0 + lane;
+        const bool in = i < wend;
+        const int b = in ? key_bucket<IdT>(keys[i], nb_valid, tail_bucket) : -1;
+        const unsigned active = __ballot_sync(kFullMask, b >= 0);
+        int ordinal = -1;
+        if (b >= 0) {
+            const unsigned peers = __match_any_sync(active, b);
+            const int before = __popc(peers & ((1u << lane) - 1u));
+            ordinal = mine[b] + before;
+            __syncwarp(active);
+            if (before == 0) mine[b] += __popc(peers);
+        }
+        __syncwarp();
+        if (in) emit(i, b, ordinal);
+    }
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kRerouteThreads)
+sparse_reroute_kernel(const IdT* ids, IdT* out, int64_t n, int L,
+                      const int32_t* __restrict__ l2p, const int32_t* __restrict__ lcnts,
+                      const int32_t* __restrict__ rqp, int D, int interleave,
+                      const int32_t* __restrict__ tile_counts) {
+    extern __shared__ __align__(128) char smem_raw[];
+    // layout: base[L] | routers[L] | warp_base[nwarps][L]
+    int32_t* base = reinterpret_cast<int32_t*>(smem_raw);
+    Router* routers = reinterpret_cast<Router*>(base + L);
+    int32_t* warp_base = reinterpret_cast<int32_t*>(routers + L);
+    const int tile = blockIdx.x;
+    for (int e = threadIdx.x; e < L; e += blockDim.x) {
+        int b = 0;
+        for (int tl = 0; tl < tile; ++tl) b += tile_counts[static_cast<int64_t>(tl) * L + e];
+        base[e] = b;
+        routers[e] = make_router(e, lcnts, rqp, D, true, interleave != 0);
+    }
+    __syncthreads();
+    // ids may alias out: every entry is read (three times) and written by the same lane, the
+    // write comes last, and tiles do not overlap.
+    tile_ordinals<IdT>(ids, n, L, false, base, warp_base, [&](int64_t i, int b, int ordinal) {
+        if (b < 0) {
+            out[i] = ids[i];
+            return;
+        }
+        const Router r = routers[b];
+        if (r.C <= 0) {
+            out[i] = ids[i];
+            return;
+        }
+        const int j = replica_index(r, b, ordinal, rqp, D, true);
+        out[i] = static_cast<IdT>(l2p[static_cast<int64_t>(b) * D + j]);
+    });
+}
+
+// Experts with C <= 0 keep their id but still consume ordinals in the count pass; the
+// reference skips them before taking an ordinal (reroute.cu:505-509), which is equivalent
+// because such an expert never maps anything.
+
+__global__ void __launch_bounds__(kRerouteThreads)
+dispatch_positions_kernel(const int32_t* __restrict__ phys, int64_t n, int P, const int32_t* __restrict__ tile_counts,
+                          int num_tiles, int32_t* __restrict__ pos, int32_t* __restrict__ expert_offsets) {
+    extern __shared__ __align__(128) char smem_raw[];
+    const int nb = P + 1;
+    // layout: base[nb] | totals[nb] | warp_base[nwarps][nb]
+    int32_t* base = reinterpret_cast<int32_t*>(smem_raw);
+    int32_t* totals = base + nb;
+    int32_t* warp_base = totals + nb;
+    __shared__ int s_carry;
+    const int tile = blockIdx.x;
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+        int before = 0, total = 0;
+        for (int tl = 0; tl < num_tiles; ++tl) {
+            const int c = tile_counts[static_cast<int64_t>(tl) * nb + b];
+            if (tl < tile) before += c;
+            total += c;
+        }
+        base[b] = before;
+        totals[b] = total;
+    }
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    // exclusive scan of totals over buckets (blocked: 256 buckets per round, warp shuffles)
+    for (int b0 = 0; b0 < nb; b0 += blockDim.x) {
+        const int b = b0 + threadIdx.x;
+        const int v = b < nb ? totals[b] : 0;
+        int incl = v;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(kFullMask, incl, d);
+            if (lane >= d) incl += o;
+        }
+        __shared__ int warp_tot[kRerouteThreads / 32];
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        int woff = 0;
+        for (int w = 0; w < warp; ++w) woff += warp_tot[w];
+        const int carry = s_carry;
+        const int excl = carry + woff + incl - v;
+        if (b < nb) {
+            base[b] += excl;
+            if (tile == 0 && expert_offsets != nullptr) expert_offsets[b] = excl;
+        }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) s_carry = carry + woff + incl;
+        __syncthreads();
+    }
+    tile_ordinals<int32_t>(phys, n, P, true, base, warp_base,
+                           [&](int64_t i, int, int ordinal) { pos[i] = ordinal; });
+}
+
+// ------------------------------------------------------------------- row gather (HBM)
+// out[i,:] = in[pos[i],:]. One elected thread per CTA drives a ring of bulk copies:
+// global -> shared (mbarrier) -> global. Rows are cut into chunks of at most kGatherChunk.
+constexpr int kGatherChunk = 16 * 1024;
+constexpr int kGatherStages = 6;
+
+__global__ void __launch_bounds__(32) gather_rows_kernel(const uint8_t* __restrict__ in, const int32_t* __restrict__ pos,
+                                                         uint8_t* __restrict__ out, int64_t num_rows,
+                                                         int64_t row_bytes, int chunks_per_row, int64_t num_src_rows,
+                                                         uint64_t timeout_ns, DeviceStatus* status) {
+    extern __shared__ __align__(128) char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[kGatherStages];
+    if (threadIdx.x != 0) return;
+    for (int s = 0; s < kGatherStages; ++s) mbar_init(&bars[s], 1);
+    fence_mbar_init();
+
+    const int64_t total = num_rows * chunks_per_row;
+    const int64_t first = blockIdx.x, step = gridDim.x;
+    const int64_t count = first < total ? (total - first + step - 1) / step : 0;
+
+    auto chunk_bytes = [&](int64_t off) -> uint32_t {
+        const int64_t left = row_bytes - off;
+        return static_cast<uint32_t>(left < kGatherChunk ? left : kGatherChunk);
+    };
+    auto issue_load = [&](int64_t k) {
+        const int64_t item = first + k * step;
+        const int64_t row = item / chunks_per_row;
+        const int64_t off = (item % chunks_per_row) * static_cast<int64_t>(kGatherChunk);
+        int64_t src_row = pos[row];
+        if (src_row < 0 || src_row >= num_src_rows) {  // never read out of bounds: record and clamp
+            report_error(status, UEP_DEV_BAD_PLAN, static_cast<int>(row));
+            src_row = 0;
+        }
+        const int s = static_cast<int>(k % kGatherStages);
+        mbar_expect_tx(&bars[s], chunk_bytes(off));
+        bulk_load(smem_raw + s * kGatherChunk, in + src_row * row_bytes + off, chunk_bytes(off), &bars[s]);
+    };
+
+    int64_t issued = count < kGatherStages - 1 ? count : kGatherStages - 1;
+    for (int64_t k = 0; k < issued; ++k) issue_load(k);
+    int64_t k = 0;
+    for (; k < count; ++k) {
+        const int s = static_cast<int>(k % kGatherStages);
+        if (!mbar_wait(&bars[s], static_cast<uint32_t>((k / kGatherStages) & 1), timeout_ns)) break;
+        const int64_t item = first + k * step;
+        const int64_t row = item / chunks_per_row;
+        const int64_t off = (item % chunks_per_row) * static_cast<int64_t>(kGatherChunk);
+        bulk_store(out + row * row_bytes + off, smem_raw + s * kGatherChunk, chunk_bytes(off));
+        bulk_commit();
+        if (issued < count) {
+            if (k >= 1) bulk_wait_read<1>();
+            issue_load(issued);
+            ++issued;
+        }
+    }
+    bulk_wait_all<0>();
+    if (k < count) {
+        // a load did not land in time: report, then give every load still in flight one more
+        // bounded wait so that shared memory is not released under it
+        report_error(status, UEP_DEV_TIMEOUT_COPY, static_cast<int>(k));
+        for (int64_t j = k; j < issued; ++j) {
+            mbar_wait(&bars[j % kGatherStages], static_cast<uint32_t>((j / kGatherStages) & 1), timeout_ns);
+        }
+    }
+}
+
+// Plain vector-load variant for rows that are not 16-byte sized/aligned multiples.
+__global__ void __launch_bounds__(256) gather_rows_plain_kernel(const uint8_t* __restrict__ in,
+                                                                const int32_t* __restrict__ pos,
+                                                                uint8_t* __restrict__ out, int64_t num_rows,
+                                                                int64_t row_bytes, int64_t num_src_rows,
+                                                                DeviceStatus* status) {
+    for (int64_t row = blockIdx.x; row < num_rows; row += gridDim.x) {
+        int64_t src = pos[row];
+        if (src < 0 || src >= num_src_rows) {
+            if (threadIdx.x == 0) report_error(status, UEP_DEV_BAD_PLAN, static_cast<int>(row));
+            src = 0;
+        }
+        for (int64_t b = threadIdx.x; b < row_bytes; b += blockDim.x) out[row * row_bytes + b] = in[src * row_bytes + b];
+    }
+}
+
+cudaError_t ensure_smem_attr(const void* fn, size_t bytes) {
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+}
+
+int dense_tiles(int T) { return (T + kDenseTileRows - 1) / kDenseTileRows; }
+int64_t sparse_tiles(int64_t n) { return (n + kSparseTileEntries - 1) / kSparseTileEntries; }
+
+template <typename IdT>
+int sparse_reroute_impl(const IdT* ids, IdT* out, int T, int K, int L, const int32_t* l2p, const int32_t* lcnts,
+                        const int32_t* rqp, int D, int interleave, int32_t* scratch, cudaStream_t stream) {
+    if (T < 0 || K < 0 || L <= 0 || D < 1) return fail(UEP_ERR_INVALID, "sparse_reroute: bad sizes");
+    const int64_t n = static_cast<int64_t>(T) * K;
+    if (n == 0) return UEP_OK;
+    if (ids == nullptr || out == nullptr || scratch == nullptr) return fail(UEP_ERR_INVALID, "sparse_reroute: null pointer");
+    const int tiles = static_cast<int>(sparse_tiles(n));
+    const size_t smem1 = sizeof(int32_t) * L;
+    const size_t smem2 = sizeof(int32_t) * L + sizeof(Router) * L + sizeof(int32_t) * (kRerouteThreads / 32) * L;
+    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(key_count_kernel<IdT>), smem1));
+    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(sparse_reroute_kernel<IdT>), smem2));
+    count_launch(2);
+    key_count_kernel<IdT><<<tiles, kRerouteThreads, smem1, stream>>>(ids, n, L, 0, scratch);
+    sparse_reroute_kernel<IdT><<<tiles, kRerouteThreads, smem2, stream>>>(ids, out, n, L, l2p, lcnts, rqp, D,
+                                                                         interleave, scratch);
+    UEP_CUDA_TRY(cudaGetLastError());
+    return UEP_OK;
+}
+
+}  // namespace
+}  // namespace uep
+
+using namespace uep;
+
+extern "C" {
+
+int64_t uep_reroute_scratch_elems(int64_t T, int K_or_0, int L) {
+    if (K_or_0 <= 0) return static_cast<int64_t>(dense_tiles(static_cast<int>(T))) * L + 4;
+    return sparse_tiles(T * K_or_0) * L + 4;
+}
+
+int uep_dense_reroute_forward(const uint8_t* routing_map, const float* probs, const int32_t* l2p,
+                              const int32_t* lcnts, const int32_t* rank_quota_prefix, uint8_t* expanded_map,
+                              float* expanded_probs, int32_t* scratch, int T, int L, int P, int D, int quota_mode,
+                              int interleave, void* stream_) {
+    if (T < 0 || L <= 0 || P <= 0 || D < 1) return fail(UEP_ERR_INVALID, "dense_reroute_forward: bad sizes");
+    if (T == 0) return UEP_OK;
+    if (!routing_map || !probs || !l2p || !lcnts || !expanded_map || !expanded_probs || !scratch ||
+        (quota_mode && !rank_quota_prefix))
+        return fail(UEP_ERR_INVALID, "dense_reroute_forward: null pointer");
+    if (D > 255) return fail(UEP_ERR_INVALID, "dense_reroute_forward: more than 255 replicas per expert");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int tiles = dense_tiles(T);
+    const int vec_ok = ((P & 3) == 0) && ((reinterpret_cast<uintptr_t>(expanded_probs) & 15u) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(expanded_map) & 3u) == 0);
+    const size_t smem = sizeof(int32_t) * P + static_cast<size_t>(kDenseTileRows) * L + 16;
+    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(dense_scatter_kernel), smem));
+    count_launch(2);
+    dense_count_kernel<<<tiles, kRerouteThreads, 0, stream>>>(routing_map, T, L, scratch);
+    dense_scatter_kernel<<<tiles, kRerouteThreads, smem, stream>>>(routing_map, probs, l2p, lcnts, rank_quota_prefix,
+                                                                   scratch, expanded_map, expanded_probs, T, L, P, D,
+                                                                   quota_mode, interleave, vec_ok);
+    UEP_CUDA_TRY(cudaGetLastError());
+    return UEP_OK;
+}
+
+int uep_dense_reroute_backward(const float* grad_expanded, const uint8_t* routing_map, const uint8_t* expanded_map,
+                               const int32_t* l2p, const int32_t* lcnts, float* grad_probs, int T, int L, int P, int D,
+                               void* stream_) {
+    if (T < 0 || L <= 0 || P <= 0 || D < 1) return fail(UEP_ERR_INVALID, "dense_reroute_backward: bad sizes");
+    if (T == 0) return UEP_OK;
+    if (!grad_expanded || !routing_map || !expanded_map || !l2p || !lcnts || !grad_probs)
+        return fail(UEP_ERR_INVALID, "dense_reroute_backward: null pointer");
+    const int64_t total = static_cast<int64_t>(T) * L;
+    int64_t blocks = (total + kRerouteThreads - 1) / kRerouteThreads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    count_launch();
+    dense_backward_kernel<<<static_cast<int>(blocks), kRerouteThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
+        grad_expanded, routing_map, expanded_map, l2p, lcnts, grad_probs, total, L, P, D);
+    UEP_CUDA_TRY(cudaGetLastError());
+    return UEP_OK;
+}
+
+int uep_sparse_reroute_i32(const int32_t* ids, int32_t* out, int T, int K, int L, const int32_t* l2p,
+                           const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
+                           int32_t* scratch, void* stream) {
+    return sparse_reroute_impl<int32_t>(ids, out, T, K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch,
+                                        static_cast<cudaStream_t>(stream));
+}
+int uep_sparse_reroute_i64(const int64_t* ids, int64_t* out, int T, int K, int L, const int32_t* l2p,
+                           const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
+                           int32_t* scratch, void* stream) {
+    return sparse_reroute_impl<long long>(reinterpret_cast<const long long*>(ids), reinterpret_cast<long long*>(out), T,
+                                          K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch,
+                                          static_cast<cudaStream_t>(stream));
+}
+
+int64_t uep_dispatch_scratch_elems(int64_t num_entries, int P) { return sparse_tiles(num_entries) * (P + 1) + 4; }
+
+int uep_dispatch_positions(const int32_t* phys_ids, int64_t num_entries, int P, int32_t* pos,
+                           int32_t* expert_offsets, int32_t* scratch, void* stream_) {
+    if (num_entries < 0 || P <= 0) return fail(UEP_ERR_INVALID, "dispatch_positions: bad sizes");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (num_entries == 0) {
+        if (expert_offsets) UEP_CUDA_TRY(cudaMemsetAsync(expert_offsets, 0, sizeof(int32_t) * (P + 1), stream));
+        return UEP_OK;
+    }
+    if (!phys_ids || !pos || !scratch) return fail(UEP_ERR_INVALID, "dispatch_positions: null pointer");
+    const int tiles = static_cast<int>(sparse_tiles(num_entries));
+    const int nb = P + 1;
+    const size_t smem1 = sizeof(int32_t) * nb;
+    const size_t smem2 = sizeof(int32_t) * nb * (2 + kRerouteThreads / 32);
+    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(key_count_kernel<int32_t>), smem1));
+    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(dispatch_positions_kernel), smem2));
+    count_launch(2);
+    key_count_kernel<int32_t><<<tiles, kRerouteThreads, smem1, stream>>>(phys_ids, num_entries, P, 1, scratch);
+    dispatch_positions_kernel<<<tiles, kRerouteThreads, smem2, stream>>>(phys_ids, num_entries, P, scratch, tiles, pos,
+                                                                         expert_offsets);
+    UEP_CUDA_TRY(cudaGetLastError());
+    return UEP_OK;
+}
+
+int uep_gather_rows(const void* in, const int32_t* pos, void* out, int64_t num_rows, int64_t num_src_rows,
+                    int64_t row_bytes, int32_t* status, void* stream_) {
+    if (num_rows < 0 || row_bytes <= 0 || num_src_rows < 0) return fail(UEP_ERR_INVALID, "gather_rows: bad sizes");
+    if (num_rows == 0) return UEP_OK;
+    if (!in || !pos || !out) return fail(UEP_ERR_INVALID, "gather_rows: null pointer");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DeviceStatus* st = reinterpret_cast<DeviceStatus*>(status);
+    const bool aligned = (row_bytes % 16 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15u) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+    count_launch();
+    if (aligned) {
+        const int chunks = static_cast<int>((row_bytes + kGatherChunk - 1) / kGatherChunk);
+        const size_t smem = static_cast<size_t>(kGatherStages) * kGatherChunk;
+        UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(gather_rows_kernel), smem));
+        int64_t ctas = num_rows * chunks;
+        if (ctas > 2 * 148) ctas = 2 * 148;
+        gather_rows_kernel<<<static_cast<int>(ctas), 32, smem, stream>>>(
+            static_cast<const uint8_t*>(in), pos, static_cast<uint8_t*>(out), num_rows, row_bytes, chunks,
+            num_src_rows, 2000000000ull, st);
+    } else {
+        int64_t ctas = num_rows > 148 * 8 ? 148 * 8 : num_rows;
+        gather_rows_plain_kernel<<<static_cast<int>(ctas), 256, 0, stream>>>(
+            static_cast<const uint8_t*>(in), pos, static_cast<uint8_t*>(out), num_rows, row_bytes, num_src_rows, st);
+    }
+    UEP_CUDA_TRY(cudaGetLastError());
+    return UEP_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,575 @@
+// Placement solver: per-expert token counts -> hot-expert replication plan, for one
+// NVLink domain, executed by one CTA (>= 4 warps).
+//
+// Results are bit-identical to the reference solver
+// (csrc/kernels/placement.cu:788-1482 of the reference): same fp32 threshold
+// arithmetic, same tie-breaks, same probe schedule of the threshold search, same
+// largest-remainder splits. The execution is different:
+//   * one lane per rank with slack / slot counters in registers for any domain size
+//     (1-3 ranks per lane), warp-wide redux instructions instead of shuffle trees,
+//     occupancy of an expert as a ballot word;
+//   * each rank's masters are ranked by counting instead of a serial insertion sort;
+//   * the per-rank load matrix is read through L2 where it is needed instead of being
+//     staged in shared memory, so shared memory stays under 48 KB at the static limits;
+//   * output arrays are cleared by the same CTA instead of six memsets.
+#pragma once
+
+#include "common.cuh"
+
+namespace uep {
+
+struct ExportEntry {
+    int expert_local;
+    int target_rank_local;
+    int quota;
+};
+
+struct SolveArgs {
+    const int32_t* global_loads;    // [L]
+    const int32_t* loads_per_rank;  // [N, L]
+    int32_t* p2l;                   // [P]
+    int32_t* l2p;                   // [L, D]
+    int32_t* lcnts;                 // [L]
+    int32_t* quota;                 // [L, D]
+    int32_t* quota_prefix;          // [L, D]
+    int32_t* rank_quota_prefix;     // [L, D]
+    int N, G, M, R, D;
+    float balance_threshold;
+    int min_tokens;
+    int allow_zero_master;
+    int locality;
+    float eps;
+    int my_rank;
+};
+
+constexpr int kSolverProbeWarps = 4;
+
+// Control words in shared memory.
+enum SolverCtrl {
+    kCtlLo = 0, kCtlHi, kCtlPrecheckDone, kCtlFastDone, kCtlNumExports, kCtlSmallRange,
+    kCtlProbe0, kCtlValid0 = kCtlProbe0 + kSolverProbeWarps, kCtlFeasible0 = kCtlValid0 + kSolverProbeWarps,
+    kCtlCount = kCtlFeasible0 + kSolverProbeWarps
+};
+
+struct SolverSmem {
+    int32_t* loads;           // [E]
+    int32_t* my_loads;        // [E]
+    int32_t* sorted_experts;  // [E]
+    int32_t* expert_slot;     // [E]
+    int32_t* rank_load;       // [Gp]
+    int32_t* source_order;    // [Gp]
+    int32_t* next_slot;       // [Gp]
+    int32_t* export_sum;      // [4][E]
+    uint32_t* occ;            // [4][E*NS]
+    ExportEntry* plan;        // [kMaxExportsPerDomain]
+    int* ctrl;                // [kCtlCount]
+};
+
+__host__ __device__ inline int solver_ns(int G) { return (G + 31) / 32; }
+__host__ __device__ inline int solver_gpad(int G) { return (G + 3) / 4 * 4; }
+__host__ __device__ inline size_t solver_smem_bytes(int E, int G) {
+    const int ns = solver_ns(G), gp = solver_gpad(G);
+    return sizeof(int32_t) * (4 * static_cast<size_t>(E) + 3 * gp + kSolverProbeWarps * static_cast<size_t>(E) +
+                              kSolverProbeWarps * static_cast<size_t>(E) * ns) +
+           sizeof(ExportEntry) * kMaxExportsPerDomain + sizeof(int) * 32;
+}
+
+__device__ inline SolverSmem carve_solver_smem(char* raw, int E, int G) {
+    const int ns = solver_ns(G), gp = solver_gpad(G);
+    SolverSmem s;
+    int32_t* p = reinterpret_cast<int32_t*>(raw);
+    s.loads = p; p += E;
+    s.my_loads = p; p += E;
+    s.sorted_experts = p; p += E;
+    s.expert_slot = p; p += E;
+    s.rank_load = p; p += gp;
+    s.source_order = p; p += gp;
+    s.next_slot = p; p += gp;
+    s.export_sum = p; p += kSolverProbeWarps * E;
+    s.occ = reinterpret_cast<uint32_t*>(p); p += kSolverProbeWarps * E * ns;
+    s.plan = reinterpret_cast<ExportEntry*>(p); p += 3 * kMaxExportsPerDomain;
+    s.ctrl = reinterpret_cast<int*>(p);
+    return s;
+}
+
+// Greedy export plan for one threshold, by one warp. Returns feasibility (uniform over
+// the warp). Semantics of csrc/kernels/placement.cu:337-667 of the reference.
+template <int NS, bool STORE>
+__device__ bool warp_build_plan(const SolverSmem& sm, int32_t* export_sum, uint32_t* occ, ExportEntry* plan,
+                                int& num_exports, int thr, int E, int G, int M, int R, int min_tokens,
+                                bool allow_zero_master, bool dynamic_floor, int lane) {
+    num_exports = 0;
+    // state init (:86-109)
+    for (int e = lane; e < E; e += kWarp) {
+        export_sum[e] = 0;
+        const int home = e / M;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) occ[e * NS + s] = ((home >> 5) == s) ? (1u << (home & 31)) : 0u;
+    }
+    int slack[NS], slots[NS];
+    int local_excess = 0, local_slack = 0;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        const int r = lane + kWarp * s;
+        const int rl = (r < G) ? sm.rank_load[r] : thr;
+        slack[s] = max(thr - rl, 0);
+        slots[s] = 0;
+        local_excess += max(rl - thr, 0);
+        local_slack += slack[s];
+    }
+    __syncwarp();
+    const int total_excess = warp_sum(local_excess);
+    const int total_slack = warp_sum(local_slack);
+    if (total_excess == 0) return true;
+    if (total_excess > total_slack) return false;
+
+    int running_excess = total_excess;
+    int running_slack = total_slack;
+    for (int ord = 0; ord < G; ++ord) {
+        const int src = sm.source_order[ord];
+        int need = max(sm.rank_load[src] - thr, 0);
+        if (need <= 0) continue;
+        if (need > running_slack) return false;
+
+        for (int pos = 0; pos < M; ++pos) {
+            const int e = sm.sorted_experts[src * M + pos];
+            const int load_e = sm.loads[e];
+            const int keep = (!allow_zero_master && load_e > 0) ? 1 : 0;
+            int es = export_sum[e];
+            int avail = max(load_e - keep - es, 0);
+            if (avail <= 0) continue;
+
+            bool my_occ[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) my_occ[s] = ((occ[e * NS + s] >> lane) & 1u) != 0u;
+            bool changed = false;
+
+            while (need > 0 && avail > 0) {
+                bool ok[NS];
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    ok[s] = (lane + kWarp * s < G) && slack[s] > 0 && slots[s] < R && !my_occ[s];
+                }
+                int floor_tokens = min_tokens;
+                if (dynamic_floor) {
+                    int feasible = 0;
+#pragma unroll
+                    for (int s = 0; s < NS; ++s) {
+                        feasible += __popc(__ballot_sync(kFullMask, ok[s] && min(min(need, slack[s]), avail) > 0));
+                    }
+                    if (feasible <= 0) break;
+                    floor_tokens = max(1, (need + feasible - 1) / feasible);
+                }
+                int cands[NS];
+                int cand = -1;
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    cands[s] = (ok[s] && min(min(need, slack[s]), avail) >= floor_tokens) ? slack[s] : -1;
+                    cand = max(cand, cands[s]);
+                }
+                const int best_cap = warp_max(cand);
+                if (best_cap < 0) break;
+                int best = -1;  // largest slack, ties to the lower rank
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    const unsigned b = __ballot_sync(kFullMask, cands[s] == best_cap);
+                    if (best < 0 && b != 0u) best = (__ffs(b) - 1) + kWarp * s;
+                }
+                if (STORE && num_exports >= kMaxExportsPerDomain) return false;
+                const int q = min(min(need, best_cap), avail);
+                if (STORE) {
+                    if (lane == 0) plan[num_exports] = ExportEntry{e, best, q};
+                    num_exports += 1;
+                }
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    if (lane + kWarp * s == best) {
+                        slack[s] -= q;
+                        slots[s] += 1;
+                        my_occ[s] = true;
+                    }
+                }
+                es += q;
+                running_excess -= q;
+                running_slack -= q;
+                need -= q;
+                avail -= q;
+                changed = true;
+            }
+            if (changed) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    const unsigned w = __ballot_sync(kFullMask, my_occ[s]);
+                    if (lane == 0) occ[e * NS + s] = w;
+                }
+                if (lane == 0) export_sum[e] = es;
+                __syncwarp();
+            }
+            if (need == 0) break;
+        }
+        if (need > 0) return false;
+        if (running_excess > running_slack) return false;
+    }
+    return true;
+}
+
+// Split of this rank's tokens of one expert over the expert's replicas, as an inclusive
+// prefix. Semantics of csrc/kernels/placement.cu:1342-1481 / :669-786 of the reference.
+template <int MAXC>
+__device__ void build_rank_quota_prefix(const SolveArgs& a, int l_global, int C, int my_load, int domain_start_rank,
+                                        int Lp, int L) {
+    const int64_t row = static_cast<int64_t>(l_global) * a.D;
+    int host_rank[MAXC], my_alloc[MAXC];
+    long long remainders[MAXC];
+    for (int j = 0; j < C; ++j) {
+        host_rank[j] = a.l2p[row + j] / Lp;
+        my_alloc[j] = 0;
+        remainders[j] = -1;
+    }
+    if (!a.locality) {
+        const int rem_my = my_load;
+        int assigned = 0, total_quota = 0;
+        for (int j = 0; j < C; ++j) total_quota += a.quota[row + j];
+        if (rem_my > 0 && total_quota > 0) {
+            for (int j = 0; j < C; ++j) {
+                const long long scaled = static_cast<long long>(rem_my) * a.quota[row + j];
+                const int share = static_cast<int>(scaled / total_quota);
+                my_alloc[j] = share;
+                remainders[j] = scaled % total_quota;
+                assigned += share;
+            }
+            int remaining = rem_my - assigned;
+            while (remaining > 0) {
+                int best_j = -1;
+                for (int j = 0; j < C; ++j) {
+                    if (best_j < 0 || remainders[j] > remainders[best_j]) best_j = j;  // ties keep the lower j
+                }
+                my_alloc[best_j] += 1;
+                remainders[best_j] = -1;
+                --remaining;
+            }
+        }
+    } else {
+        int remote_cap[MAXC];
+        int host_left[MAXC];  // remaining own load of host_rank[j]'s rank, shared between equal hosts via `first`
+        int first[MAXC];
+        int rem_my = my_load;
+        int total_remote_cap = 0;
+        for (int j = 0; j < C; ++j) {
+            int f = j;
+            for (int u = 0; u < j; ++u) {
+                if (host_rank[u] == host_rank[j]) {
+                    f = first[u];
+                    break;
+                }
+            }
+            first[j] = f;
+            if (f == j) {
+                host_left[j] = __ldcg(a.loads_per_rank + static_cast<int64_t>(host_rank[j]) * L + l_global);
+            }
+            const int q = a.quota[row + j];
+            const int local_fill = min(host_left[f], q);
+            host_left[f] -= local_fill;
+            remote_cap[j] = q - local_fill;
+            total_remote_cap += remote_cap[j];
+            if (host_rank[j] == a.my_rank) {
+                my_alloc[j] += local_fill;
+                rem_my -= local_fill;
+            }
+        }
+        (void)domain_start_rank;
+        rem_my = max(rem_my, 0);
+        if (rem_my > 0 && total_remote_cap > 0) {
+            int assigned = 0;
+            for (int j = 0; j < C; ++j) {
+                if (host_rank[j] == a.my_rank || remote_cap[j] <= 0) continue;
+                const long long scaled = static_cast<long long>(rem_my) * remote_cap[j];
+                const int share = static_cast<int>(scaled / total_remote_cap);
+                my_alloc[j] += share;
+                remainders[j] = scaled % total_remote_cap;
+                assigned += share;
+            }
+            int remaining = rem_my - assigned;
+            while (remaining > 0) {
+                int best_j = -1;
+                for (int j = 0; j < C; ++j) {
+                    if (host_rank[j] == a.my_rank || remote_cap[j] <= 0) continue;
+                    if (best_j < 0 || remainders[j] > remainders[best_j] ||
+                        (remainders[j] == remainders[best_j] &&
+                         (host_rank[j] < host_rank[best_j] || (host_rank[j] == host_rank[best_j] && j < best_j)))) {
+                        best_j = j;
+                    }
+                }
+                if (best_j < 0) break;
+                my_alloc[best_j] += 1;
+                remainders[best_j] = -1;
+                --remaining;
+            }
+        }
+    }
+    int prefix = 0;
+    for (int j = 0; j < C; ++j) {
+        prefix += my_alloc[j];
+        a.rank_quota_prefix[row + j] = prefix;
+    }
+}
+
+// Solve one NVLink domain. All threads of the CTA must call it (blockDim.x >= 128,
+// multiple of 32). smem_raw must hold solver_smem_bytes(E, G) bytes, 16-byte aligned.
+template <int NS>
+__device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, DeviceStatus* status) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int G = a.G, M = a.M, R = a.R, D = a.D;
+    const int E = G * M, Lp = M + R, L = a.N * M;
+    const int domain_start_rank = domain * G;
+    const int domain_start_log = domain_start_rank * M;
+    SolverSmem sm = carve_solver_smem(smem_raw, E, G);
+
+    // Clear this domain's slice of every output, then place the masters.
+    for (int i = tid; i < G * Lp; i += nthreads) a.p2l[domain_start_rank * Lp + i] = -1;
+    for (int i = tid; i < E * D; i += nthreads) {
+        const int64_t idx = static_cast<int64_t>(domain_start_log) * D + i;
+        a.l2p[idx] = -1;
+        a.quota[idx] = 0;
+        a.quota_prefix[idx] = 0;
+        a.rank_quota_prefix[idx] = 0;
+    }
+    __syncthreads();
+    for (int i = tid; i < E; i += nthreads) {
+        const int l_global = domain_start_log + i;
+        sm.loads[i] = __ldcg(a.global_loads + l_global);
+        sm.my_loads[i] = __ldcg(a.loads_per_rank + static_cast<int64_t>(a.my_rank) * L + l_global);
+        sm.expert_slot[i] = 1;
+        const int phys = (domain_start_rank + i / M) * Lp + i % M;
+        a.p2l[phys] = l_global;
+        a.l2p[static_cast<int64_t>(l_global) * D] = phys;
+    }
+    __syncthreads();
+    for (int r = tid; r < G; r += nthreads) {
+        int sum = 0;
+        for (int m = 0; m < M; ++m) sum += sm.loads[r * M + m];
+        sm.rank_load[r] = sum;
+        sm.next_slot[r] = 0;
+    }
+    __syncthreads();
+    // ranks by load descending, ties to the lower index; each rank's masters likewise
+    for (int i = tid; i < G; i += nthreads) {
+        const int mine = sm.rank_load[i];
+        int pos = 0;
+        for (int j = 0; j < G; ++j) {
+            const int other = sm.rank_load[j];
+            pos += (other > mine || (other == mine && j < i)) ? 1 : 0;
+        }
+        sm.source_order[pos] = i;
+    }
+    for (int i = tid; i < E; i += nthreads) {
+        const int base = (i / M) * M;
+        const int mine = sm.loads[i];
+        int pos = 0;
+        for (int j = base; j < base + M; ++j) {
+            const int other = sm.loads[j];
+            pos += (other > mine || (other == mine && j < i)) ? 1 : 0;
+        }
+        sm.sorted_experts[base + pos] = i;
+    }
+    const bool do_search = (R > 0 && G > 1);
+    if (tid == 0) {
+        sm.ctrl[kCtlNumExports] = 0;
+        sm.ctrl[kCtlFastDone] = 0;
+        sm.ctrl[kCtlPrecheckDone] = 0;
+        if (do_search) {
+            int total = 0, mx = 0;
+            for (int r = 0; r < G; ++r) {
+                total += sm.rank_load[r];
+                mx = max(mx, sm.rank_load[r]);
+            }
+            // fp32, in the reference's order: ceilf((float(total) / G) * bt)
+            const float bt = fmaxf(a.balance_threshold, 1.0f);
+            const float mean = __fdiv_rn(static_cast<float>(total), static_cast<float>(G));
+            const int lo = static_cast<int>(ceilf(__fmul_rn(mean, bt)));
+            sm.ctrl[kCtlLo] = lo;
+            sm.ctrl[kCtlHi] = max(mx, lo);
+        }
+    }
+    __syncthreads();
+
+    const bool allow0 = a.allow_zero_master != 0;
+    if (do_search) {
+        if (warp == 0) {  // fast path: up to three builds with the dynamic floor
+            const int lo = sm.ctrl[kCtlLo], hi = sm.ctrl[kCtlHi];
+            const float eps = fmaxf(a.eps, 0.0f);
+            int thr = static_cast<int>(ceilf(__fmul_rn(static_cast<float>(lo), __fadd_rn(1.0f, eps))));
+            thr = max(thr, lo);
+            const int step = max(1, (hi + 99) / 100);
+            bool done = false;
+            for (int retry = 0; retry <= 2 && !done; ++retry) {
+                int n = 0;
+                done = warp_build_plan<NS, true>(sm, sm.export_sum, sm.occ, sm.plan, n, thr, E, G, M, R, a.min_tokens,
+                                                 allow0, true, lane);
+                if (done) {
+                    if (lane == 0) {
+                        sm.ctrl[kCtlNumExports] = n;
+                        sm.ctrl[kCtlFastDone] = 1;
+                        sm.ctrl[kCtlLo] = thr;
+                    }
+                } else {
+                    thr = min(hi, thr + step);
+                }
+                __syncwarp();
+            }
+        }
+        __syncthreads();
+        if (!sm.ctrl[kCtlFastDone]) {
+            if (warp == 0) {
+                int lo = sm.ctrl[kCtlLo], hi = sm.ctrl[kCtlHi];
+                while (lo < hi) {  // capacity bisection
+                    const int probe = lo + ((hi - lo) >> 1);
+                    int ex = 0, sl = 0;
+                    for (int r = lane; r < G; r += kWarp) {
+                        ex += max(sm.rank_load[r] - probe, 0);
+                        sl += max(probe - sm.rank_load[r], 0);
+                    }
+                    if (warp_sum(ex) <= warp_sum(sl)) hi = probe;
+                    else lo = probe + 1;
+                }
+                int n = 0;
+                const bool ok = warp_build_plan<NS, true>(sm, sm.export_sum, sm.occ, sm.plan, n, lo, E, G, M, R,
+                                                          a.min_tokens, allow0, false, lane);
+                if (lane == 0) {
+                    sm.ctrl[kCtlPrecheckDone] = ok ? 1 : 0;
+                    if (ok) {
+                        sm.ctrl[kCtlNumExports] = n;
+                        sm.ctrl[kCtlLo] = lo;
+                    } else {
+                        sm.ctrl[kCtlLo] = min(lo + 1, sm.ctrl[kCtlHi]);
+                    }
+                }
+            }
+            __syncthreads();
+            while (true) {
+                if (sm.ctrl[kCtlPrecheckDone] || sm.ctrl[kCtlLo] >= sm.ctrl[kCtlHi]) break;
+                __syncthreads();  // everyone has read lo/hi before thread 0 rewrites the probe table
+                if (tid == 0) {
+                    const int lo = sm.ctrl[kCtlLo], hi = sm.ctrl[kCtlHi];
+                    const int range = hi - lo;
+                    const int small_range = (range <= kSolverProbeWarps) ? 1 : 0;
+                    sm.ctrl[kCtlSmallRange] = small_range;
+                    for (int w = 0; w < kSolverProbeWarps; ++w) {
+                        if (small_range) {
+                            sm.ctrl[kCtlProbe0 + w] = lo + w;
+                            sm.ctrl[kCtlValid0 + w] = (lo + w < hi) ? 1 : 0;
+                        } else {
+                            sm.ctrl[kCtlProbe0 + w] =
+                                lo + static_cast<int>((static_cast<long long>(range) * (w + 1)) / (kSolverProbeWarps + 1));
+                            sm.ctrl[kCtlValid0 + w] = 1;
+                        }
+                        sm.ctrl[kCtlFeasible0 + w] = 0;
+                    }
+                }
+                __syncthreads();
+                if (warp < kSolverProbeWarps && sm.ctrl[kCtlValid0 + warp]) {
+                    int n = 0;
+                    const bool ok = warp_build_plan<NS, false>(sm, sm.export_sum + warp * E, sm.occ + warp * E * NS,
+                                                               nullptr, n, sm.ctrl[kCtlProbe0 + warp], E, G, M, R,
+                                                               a.min_tokens, allow0, false, lane);
+                    if (lane == 0) sm.ctrl[kCtlFeasible0 + warp] = ok ? 1 : 0;
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    if (sm.ctrl[kCtlSmallRange]) {
+                        int best = -1;
+                        for (int w = 0; w < kSolverProbeWarps; ++w) {
+                            if (sm.ctrl[kCtlValid0 + w] && sm.ctrl[kCtlFeasible0 + w]) {
+                                best = sm.ctrl[kCtlProbe0 + w];
+                                break;
+                            }
+                        }
+                        if (best >= 0) {
+                            sm.ctrl[kCtlLo] = best;
+                            sm.ctrl[kCtlHi] = best;
+                        } else {
+                            sm.ctrl[kCtlLo] = sm.ctrl[kCtlHi];
+                        }
+                    } else {
+                        int first = -1;
+                        for (int w = 0; w < kSolverProbeWarps; ++w) {
+                            if (sm.ctrl[kCtlFeasible0 + w]) {
+                                first = w;
+                                break;
+                            }
+                        }
+                        if (first >= 0) {
+                            sm.ctrl[kCtlHi] = sm.ctrl[kCtlProbe0 + first];
+                            if (first > 0) sm.ctrl[kCtlLo] = sm.ctrl[kCtlProbe0 + first - 1] + 1;
+                        } else {
+                            sm.ctrl[kCtlLo] = sm.ctrl[kCtlProbe0 + kSolverProbeWarps - 1] + 1;
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+            if (!sm.ctrl[kCtlPrecheckDone]) {
+                if (warp == 0) {
+                    int n = 0;
+                    const bool ok = warp_build_plan<NS, true>(sm, sm.export_sum, sm.occ, sm.plan, n, sm.ctrl[kCtlLo], E,
+                                                              G, M, R, a.min_tokens, allow0, false, lane);
+                    if (lane == 0) {
+                        sm.ctrl[kCtlNumExports] = ok ? n : 0;
+                        if (!ok) report_error(status, UEP_DEV_SOLVER_INFEASIBLE, sm.ctrl[kCtlLo]);
+                    }
+                }
+                __syncthreads();
+            }
+        }
+    }
+
+    // Emit: master quotas, then replicas in plan order.
+    for (int e = tid; e < E; e += nthreads) {
+        const int64_t row = static_cast<int64_t>(domain_start_log + e) * D;
+        a.quota[row] = do_search ? (sm.loads[e] - sm.export_sum[e]) : sm.loads[e];
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const int n = sm.ctrl[kCtlNumExports];
+        for (int k = 0; k < n; ++k) {
+            const ExportEntry entry = sm.plan[k];
+            const int l_global = domain_start_log + entry.expert_local;
+            const int64_t row = static_cast<int64_t>(l_global) * D;
+            const int slot = sm.expert_slot[entry.expert_local]++;
+            const int phys =
+                (domain_start_rank + entry.target_rank_local) * Lp + M + sm.next_slot[entry.target_rank_local]++;
+            if (slot >= D || phys >= (domain_start_rank + entry.target_rank_local + 1) * Lp) {
+                report_error(status, UEP_DEV_BAD_PLAN, k);
+                continue;
+            }
+            a.p2l[phys] = l_global;
+            a.l2p[row + slot] = phys;
+            a.quota[row + slot] = entry.quota;
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += nthreads) {
+        const int l_global = domain_start_log + e;
+        const int64_t row = static_cast<int64_t>(l_global) * D;
+        const int C = min(sm.expert_slot[e], D);
+        a.lcnts[l_global] = C;
+        int prefix = 0;
+        for (int j = 0; j < C; ++j) {
+            prefix += a.quota[row + j];
+            a.quota_prefix[row + j] = prefix;
+        }
+        if (C <= 8) build_rank_quota_prefix<8>(a, l_global, C, sm.my_loads[e], domain_start_rank, Lp, L);
+        else build_rank_quota_prefix<kMaxRanksPerDomain>(a, l_global, C, sm.my_loads[e], domain_start_rank, Lp, L);
+    }
+    __syncthreads();
+}
+
+__device__ inline void solve_domain_dispatch(const SolveArgs& a, int domain, char* smem_raw, DeviceStatus* status) {
+    const int ns = solver_ns(a.G);
+    if (ns == 1) solve_domain<1>(a, domain, smem_raw, status);
+    else if (ns == 2) solve_domain<2>(a, domain, smem_raw, status);
+    else solve_domain<3>(a, domain, smem_raw, status);
+}
+
+}  // namespace uep
