@@ -1,0 +1,308 @@
+// Kernel 3 — weight_sync: every replicated local master expert (weights and scales) is
+// pushed into the replica slots of its peers, straight from the stored plan.
+//
+// The reference first builds a task list with a single-thread kernel and then runs a
+// thread-copy kernel (16-byte loads, streaming stores) when the NVLink domain has at most
+// 8 ranks, or a two-stage bulk-copy kernel above that (csrc/kernels/weight_sync.cu:205-522,
+// 714-775, 782-986 of the reference). Here there is no task list and one kernel:
+//   * every CTA derives the send list from the plan rows of this rank's masters
+//     (l2p / lcnts) with a block-wide scan, a few hundred nanoseconds of work;
+//   * one elected thread per CTA drives a 4-stage ring of 32 KiB bulk copies: the tile is
+//     read from local HBM once (cp.async.bulk global->shared, mbarrier) and stored to each
+//     destination slot (cp.async.bulk shared->global, peer memory over NVLink); loads run
+//     up to three tiles ahead of the stores;
+//   * tiles are interleaved over masters so that concurrent CTAs feed different peers;
+//   * the CTA that finishes last publishes "rank r has delivered epoch e" to the ranks it
+//     sent to (system-scope release) and waits, bounded, for the same word from the ranks
+//     that send to it. When the kernel ends, this rank's replica slots are complete.
+// Pointers or sizes that are not multiples of 16 bytes take a plain vector/byte copy path.
+
+#include "internal.h"
+
+namespace uep {
+
+namespace {
+
+constexpr int kSyncThreads = 128;
+constexpr int kSyncTile = 32 * 1024;
+constexpr int kSyncStages = 4;
+constexpr int kMaxSends = kMaxExportsPerDomain;  // replicas of one rank's masters never exceed G*R <= 512
+
+struct SyncShared {
+    int n_active;          // masters of this rank that have replicas
+    int total_reps;        // sum of their replica counts
+    int all_aligned;       // every source pointer 16-byte aligned
+    int is_last;
+    unsigned send_mask[3]; // ranks this rank sends to
+    unsigned recv_mask[3]; // ranks that send to this rank
+    int timeout_peer;
+    short active_master[kMaxExpertsPerDomain];  // [n_active] local master index
+    short rep_start[kMaxExpertsPerDomain + 1];  // [n_active+1] offsets into rep_*
+    short rep_rank[kMaxSends];
+    short rep_slot[kMaxSends];
+};
+
+struct TileRef {
+    int active;      // index into active_master
+    int shard;       // 0..3
+    int64_t offset;  // byte offset inside the shard
+    int bytes;       // bytes of this tile
+};
+
+__device__ __forceinline__ TileRef decode_tile(int64_t idx, int n_active, const ShardLayout& sh, const int* shard_tiles) {
+    TileRef t;
+    t.active = static_cast<int>(idx % n_active);
+    int tile = static_cast<int>(idx / n_active);
+    t.shard = 0;
+    while (t.shard < sh.num_shards - 1 && tile >= shard_tiles[t.shard]) {
+        tile -= shard_tiles[t.shard];
+        ++t.shard;
+    }
+    t.offset = static_cast<int64_t>(tile) * kSyncTile;
+    const int64_t left = sh.bytes[t.shard] - t.offset;
+    t.bytes = static_cast<int>(left < kSyncTile ? left : kSyncTile);
+    return t;
+}
+
+__device__ __forceinline__ uint8_t* dest_addr(const RankDev& rk, const ShardLayout& sh, int shard, int rank, int slot) {
+    if (shard < 2) return rk.peer_replica_weight[rank] + static_cast<int64_t>(slot) * sh.weight_slot_stride + sh.slot_offset[shard];
+    return rk.peer_replica_scale[rank] + static_cast<int64_t>(slot) * sh.scale_slot_stride + sh.slot_offset[shard];
+}
+
+__device__ void copy_plain(const uint8_t* src, uint8_t* dst, int bytes) {
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+    int done = 0;
+    if (vec) {
+        const int nvec = bytes / 16;
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            st_global_cs_v4(dst + static_cast<int64_t>(i) * 16, ld_global_nc_v4(src + static_cast<int64_t>(i) * 16));
+        }
+        done = nvec * 16;
+    }
+    for (int i = done + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call) {
+    extern __shared__ __align__(128) char smem_raw[];  // kSyncStages * kSyncTile
+    __shared__ SyncShared sm;
+    __shared__ __align__(8) uint64_t bars[kSyncStages];
+    __shared__ int shard_tiles[4];
+
+    const int local = blockIdx.x / call.ctas_per_rank;
+    const int cta = blockIdx.x % call.ctas_per_rank;
+    const RankDev& rk = *call.rank[local];
+    const PlanPtrs& plan = call.plan[local];
+    const ShardLayout& sh = call.shards;
+    const int me = rk.my_rank, M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N;
+    const int tid = threadIdx.x;
+
+    // ---- setup: send list of this rank from the plan ---------------------------------
+    if (tid == 0) {
+        sm.n_active = 0;
+        sm.total_reps = 0;
+        sm.all_aligned = 1;
+        sm.is_last = 0;
+        sm.timeout_peer = -1;
+        for (int w = 0; w < 3; ++w) sm.send_mask[w] = sm.recv_mask[w] = 0;
+        for (int s = 0; s < 4; ++s) shard_tiles[s] = s < sh.num_shards ? static_cast<int>((sh.bytes[s] + kSyncTile - 1) / kSyncTile) : 0;
+        for (int s = 0; s < kSyncStages; ++s) mbar_init(&bars[s], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    // blocked scan over masters: active index and replica offsets
+    for (int m0 = 0; m0 < M; m0 += blockDim.x) {
+        const int m = m0 + tid;
+        int reps = 0;
+        if (m < M) {
+            reps = plan.lcnts[me * M + m] - 1;
+            reps = reps < 0 ? 0 : (reps > D - 1 ? D - 1 : reps);
+        }
+        const int act = reps > 0 ? 1 : 0;
+        // warp-level inclusive scans, then across warps through shared memory
+        int a_incl = act, r_incl = reps;
+        const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int oa = __shfl_up_sync(kFullMask, a_incl, d), orr = __shfl_up_sync(kFullMask, r_incl, d);
+            if (lane >= d) {
+                a_incl += oa;
+                r_incl += orr;
+            }
+        }
+        __shared__ int w_a[kSyncThreads / 32], w_r[kSyncThreads / 32];
+        if (lane == 31) {
+            w_a[warp] = a_incl;
+            w_r[warp] = r_incl;
+        }
+        __syncthreads();
+        int a_off = sm.n_active, r_off = sm.total_reps;
+        for (int w = 0; w < warp; ++w) {
+            a_off += w_a[w];
+            r_off += w_r[w];
+        }
+        if (act) {
+            const int ai = a_off + a_incl - 1;
+            const int rs = r_off + r_incl - reps;
+            sm.active_master[ai] = static_cast<short>(m);
+            sm.rep_start[ai] = static_cast<short>(rs);
+            const int l = me * M + m;
+            for (int j = 0; j < reps && rs + j < kMaxSends; ++j) {
+                const int phys = plan.l2p[static_cast<int64_t>(l) * D + 1 + j];
+                int drank = phys / Lp, dslot = phys % Lp - M;
+                if (phys < 0 || drank >= N || dslot < 0 || dslot >= R) {  // never store outside a slot table
+                    report_error(rk.status, UEP_DEV_BAD_PLAN, l);
+                    drank = -1;
+                    dslot = 0;
+                } else {
+                    atomicOr(&sm.send_mask[drank >> 5], 1u << (drank & 31));
+                }
+                sm.rep_rank[rs + j] = static_cast<short>(drank);
+                sm.rep_slot[rs + j] = static_cast<short>(dslot);
+            }
+            // source alignment
+            for (int s = 0; s < sh.num_shards; ++s) {
+                if (sh.bytes[s] == 0) continue;
+                const uintptr_t p = static_cast<uintptr_t>(call.src_ptrs[local][s][m]);
+                if (p & 15u) atomicAnd(&sm.all_aligned, 0);
+            }
+        }
+        __syncthreads();
+        if (tid == blockDim.x - 1) {
+            sm.n_active = a_off + a_incl;
+            sm.total_reps = r_off + r_incl;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxSends ? sm.total_reps : kMaxSends);
+    for (int s = tid; s < R; s += blockDim.x) {
+        const int l = plan.p2l[me * Lp + M + s];
+        if (l >= 0) {
+            const int src = l / M;
+            if (src >= 0 && src < N && src != me) atomicOr(&sm.recv_mask[src >> 5], 1u << (src & 31));
+        }
+    }
+    __syncthreads();
+
+    // ---- copy -------------------------------------------------------------------------
+    int tiles_per_expert = 0;
+    for (int s = 0; s < sh.num_shards; ++s) tiles_per_expert += shard_tiles[s];
+    const int64_t total_tiles = static_cast<int64_t>(sm.n_active) * tiles_per_expert;
+    const int64_t first = cta, step = call.ctas_per_rank;
+    const int64_t count = first < total_tiles ? (total_tiles - first + step - 1) / step : 0;
+
+    if (sm.all_aligned) {
+        if (tid == 0) {
+            auto issue_load = [&](int64_t k) {
+                const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
+                const int m = sm.active_master[t.active];
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(call.src_ptrs[local][t.shard][m]) + t.offset;
+                const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
+                const int s = static_cast<int>(k % kSyncStages);
+                if (bytes16) {
+                    mbar_expect_tx(&bars[s], bytes16);
+                    bulk_load(smem_raw + s * kSyncTile, src, bytes16, &bars[s]);
+                }
+            };
+            int64_t issued = count < kSyncStages - 1 ? count : kSyncStages - 1;
+            for (int64_t k = 0; k < issued; ++k) issue_load(k);
+            int64_t k = 0;
+            for (; k < count; ++k) {
+                const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
+                const int m = sm.active_master[t.active];
+                const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
+                const int s = static_cast<int>(k % kSyncStages);
+                if (bytes16 && !mbar_wait(&bars[s], static_cast<uint32_t>((k / kSyncStages) & 1), call.timeout_ns)) break;
+                const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
+                for (int r = r0; r < r1; ++r) {
+                    if (sm.rep_rank[r] < 0) continue;
+                    uint8_t* dst = dest_addr(rk, sh, t.shard, sm.rep_rank[r], sm.rep_slot[r]) + t.offset;
+                    if (bytes16) bulk_store(dst, smem_raw + s * kSyncTile, bytes16);
+                    if (static_cast<uint32_t>(t.bytes) != bytes16) {  // up to 15 trailing bytes of a shard
+                        const uint8_t* src = reinterpret_cast<const uint8_t*>(call.src_ptrs[local][t.shard][m]) + t.offset;
+                        for (int b = bytes16; b < t.bytes; ++b) dst[b] = src[b];
+                    }
+                }
+                bulk_commit();
+                if (issued < count) {
+                    if (k >= 1) bulk_wait_read<1>();
+                    issue_load(issued);
+                    ++issued;
+                }
+            }
+            bulk_wait_all<0>();
+            if (k < count) {
+                report_error(rk.status, UEP_DEV_TIMEOUT_COPY, static_cast<int>(k));
+                for (int64_t j = k; j < issued; ++j) {
+                    mbar_wait(&bars[j % kSyncStages], static_cast<uint32_t>((j / kSyncStages) & 1), call.timeout_ns);
+                }
+            }
+        }
+    } else {
+        for (int64_t k = 0; k < count; ++k) {
+            const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
+            const int m = sm.active_master[t.active];
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(call.src_ptrs[local][t.shard][m]) + t.offset;
+            const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
+            for (int r = r0; r < r1; ++r) {
+                if (sm.rep_rank[r] < 0) continue;
+                copy_plain(src, dest_addr(rk, sh, t.shard, sm.rep_rank[r], sm.rep_slot[r]) + t.offset, t.bytes);
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+
+    // ---- completion: last CTA of the rank signals its receivers and waits for its senders
+    if (tid == 0) {
+        const int ticket = atomicAdd(rk.sync_ticket, 1);
+        if (ticket == call.ctas_per_rank - 1) {
+            *rk.sync_ticket = 0;
+            sm.is_last = 1;
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (!sm.is_last) return;
+    for (int p = tid; p < N; p += blockDim.x) {
+        if (sm.send_mask[p >> 5] & (1u << (p & 31))) st_release_sys_u64(rk.peer_sync_flags[p] + me, call.epoch);
+    }
+    for (int p = tid; p < N; p += blockDim.x) {
+        if (sm.recv_mask[p >> 5] & (1u << (p & 31))) {
+            if (!wait_flag_ge(rk.peer_sync_flags[me] + p, call.epoch, call.timeout_ns)) atomicMax(&sm.timeout_peer, p);
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && sm.timeout_peer >= 0) report_error(rk.status, UEP_DEV_TIMEOUT_SYNC, sm.timeout_peer);
+}
+
+}  // namespace
+
+int weight_sync_max_ctas_per_rank(int nlocal, int num_sms) {
+    // one CTA per SM (128 KiB of shared memory each); hosted ranks share the device
+    const int per = num_sms / (nlocal > 0 ? nlocal : 1);
+    return per < 1 ? 1 : per;
+}
+
+cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(kSyncStages) * kSyncTile;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(weight_sync_kernel),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const dim3 grid(call.nlocal * call.ctas_per_rank), block(kSyncThreads);
+    count_launch();
+    if (call.nlocal > 1) {
+        // hosted ranks wait for each other's completion words: they must be co-resident
+        SyncCall copy = call;
+        void* args[] = {&copy};
+        return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(weight_sync_kernel), grid, block, args, smem,
+                                           stream);
+    }
+    weight_sync_kernel<<<grid, block, smem, stream>>>(call);
+    return cudaGetLastError();
+}
+
+}  // namespace uep
