@@ -260,6 +260,13 @@ void uep_event_destroy(uep_event* ev);
 int uep_poll_status(uep_manager* m, int local_rank, int* code, int* detail);
 int uep_clear_status(uep_manager* m);
 
+/* Failure-detection test hook, host side only: from the next call on, the hosted rank `rank`
+ * completes its work but does not publish its exchange / completion flags, so the ranks
+ * that wait for it run into their time limit and report UEP_DEV_TIMEOUT_*; -1 switches the
+ * hook off. No device fault is involved. No counterpart in the reference (its waits are
+ * unbounded, csrc/kernels/weight_sync.cu:666-677, csrc/kernels/ptx.cuh:73-86). */
+int uep_debug_withhold_rank(uep_manager* m, int rank);
+
 /* Counters for benchmarks: kernels launched by this library since the last reset. */
 int64_t uep_launch_count(void);
 void uep_reset_launch_count(void);

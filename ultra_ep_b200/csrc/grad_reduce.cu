@@ -1,0 +1,287 @@
+// Kernel 4 — replica Wgrad reduce: for every local master that has replicas,
+//     master = ((master + g_1) + g_2) + ...      (fp32, replicas in plan slot order)
+// where g_j is read from the peer that hosts replica j, and every consumed replica region
+// is overwritten with zeros. The order is fixed, so the result is bit-exact and equal to
+// the reference's deterministic kernel (csrc/kernels/grad_reduce.cu:289-394 of the
+// reference; task order :41-69).
+//
+// The reference builds a task list with a single-thread kernel, then per tile loads one
+// replica sub-tile at a time through a single shared-memory buffer (load, wait, add, zero
+// with per-thread stores, repeat). Here:
+//   * no task list: every CTA derives the pull list from the plan rows with a block scan;
+//   * accumulators live in registers (8 floats per thread per 8 KiB tile);
+//   * an elected thread keeps a 6-stage ring of bulk loads from peer memory in flight, so
+//     the NVLink latency of replica j+1 .. j+5 (and of the next tiles) is hidden behind the
+//     add of replica j;
+//   * the consumed region is zeroed with one bulk store from a zero-filled shared buffer
+//     instead of 256 threads of vector stores;
+//   * tiles are interleaved over masters so that concurrent CTAs pull from different peers.
+// The CTA budget (SMs used while the backward pass runs next to it) and the 56 KiB of
+// shared memory per CTA keep room for compute kernels on the same SMs.
+
+#include "internal.h"
+
+namespace uep {
+
+namespace {
+
+constexpr int kReduceThreads = 256;
+constexpr int kReduceTileElems = 2048;  // 8 KiB
+constexpr int kReduceTileBytes = kReduceTileElems * 4;
+constexpr int kReduceStages = 6;
+constexpr int kMaxPulls = kMaxExportsPerDomain;
+
+struct ReduceShared {
+    int n_active, total_reps, vector_ok, error;
+    short active_master[kMaxExpertsPerDomain];
+    short rep_start[kMaxExpertsPerDomain + 1];
+    short rep_rank[kMaxPulls];
+    short rep_slot[kMaxPulls];
+};
+
+struct ReduceItem {
+    int active;       // index into active_master
+    int shard;        // 0 fc1, 1 fc2
+    int64_t offset;   // element offset inside the shard
+    int elems;
+};
+
+__device__ __forceinline__ ReduceItem decode_item(int64_t idx, int n_active, int64_t fc1_numel, int64_t fc2_numel,
+                                                  int tiles_fc1) {
+    ReduceItem it;
+    it.active = static_cast<int>(idx % n_active);
+    const int tile = static_cast<int>(idx / n_active);
+    it.shard = tile < tiles_fc1 ? 0 : 1;
+    const int t = it.shard == 0 ? tile : tile - tiles_fc1;
+    it.offset = static_cast<int64_t>(t) * kReduceTileElems;
+    const int64_t left = (it.shard == 0 ? fc1_numel : fc2_numel) - it.offset;
+    it.elems = static_cast<int>(left < kReduceTileElems ? left : kReduceTileElems);
+    return it;
+}
+
+__global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall call) {
+    extern __shared__ __align__(128) char smem_raw[];  // [kReduceStages + 1] tiles; the last one stays zero
+    __shared__ ReduceShared sm;
+    __shared__ __align__(8) uint64_t bars[kReduceStages];
+
+    const int local = blockIdx.x / call.ctas_per_rank;
+    const int cta = blockIdx.x % call.ctas_per_rank;
+    const RankDev& rk = *call.rank[local];
+    const PlanPtrs& plan = call.plan[local];
+    const int me = rk.my_rank, M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N;
+    const int tid = threadIdx.x;
+    const int64_t fc1 = call.fc1_numel, fc2 = call.fc2_numel, total_numel = fc1 + fc2;
+    float* zero_tile = reinterpret_cast<float*>(smem_raw + kReduceStages * kReduceTileBytes);
+
+    if (tid == 0) {
+        sm.n_active = 0;
+        sm.total_reps = 0;
+        sm.vector_ok = ((fc1 & 3) == 0 && (fc2 & 3) == 0) ? 1 : 0;
+        sm.error = 0;
+        for (int s = 0; s < kReduceStages; ++s) mbar_init(&bars[s], 1);
+        fence_mbar_init();
+    }
+    for (int i = tid; i < kReduceTileElems; i += blockDim.x) zero_tile[i] = 0.f;
+    fence_proxy_async_smem();
+    __syncthreads();
+
+    // pull list: masters of this rank with replicas, and where each replica lives
+    for (int m0 = 0; m0 < M; m0 += blockDim.x) {
+        const int m = m0 + tid;
+        int reps = 0;
+        if (m < M) {
+            reps = plan.lcnts[me * M + m] - 1;
+            reps = reps < 0 ? 0 : (reps > D - 1 ? D - 1 : reps);
+        }
+        const int act = reps > 0 ? 1 : 0;
+        int a_incl = act, r_incl = reps;
+        const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int oa = __shfl_up_sync(kFullMask, a_incl, d), orr = __shfl_up_sync(kFullMask, r_incl, d);
+            if (lane >= d) {
+                a_incl += oa;
+                r_incl += orr;
+            }
+        }
+        __shared__ int w_a[kReduceThreads / 32], w_r[kReduceThreads / 32];
+        if (lane == 31) {
+            w_a[warp] = a_incl;
+            w_r[warp] = r_incl;
+        }
+        __syncthreads();
+        int a_off = sm.n_active, r_off = sm.total_reps;
+        for (int w = 0; w < warp; ++w) {
+            a_off += w_a[w];
+            r_off += w_r[w];
+        }
+        if (act) {
+            const int ai = a_off + a_incl - 1;
+            const int rs = r_off + r_incl - reps;
+            sm.active_master[ai] = static_cast<short>(m);
+            sm.rep_start[ai] = static_cast<short>(rs);
+            const int l = me * M + m;
+            for (int j = 0; j < reps && rs + j < kMaxPulls; ++j) {
+                const int phys = plan.l2p[static_cast<int64_t>(l) * D + 1 + j];
+                int prank = phys / Lp, pslot = phys % Lp - M;
+                if (phys < 0 || prank >= N || pslot < 0 || pslot >= R) {
+                    report_error(rk.status, UEP_DEV_BAD_PLAN, l);
+                    prank = -1;
+                    pslot = 0;
+                }
+                sm.rep_rank[rs + j] = static_cast<short>(prank);
+                sm.rep_slot[rs + j] = static_cast<short>(pslot);
+            }
+            if ((static_cast<uintptr_t>(call.fc1_grad_ptrs[local][m]) & 15u) ||
+                (static_cast<uintptr_t>(call.fc2_grad_ptrs[local][m]) & 15u)) {
+                atomicAnd(&sm.vector_ok, 0);
+            }
+        }
+        __syncthreads();
+        if (tid == blockDim.x - 1) {
+            sm.n_active = a_off + a_incl;
+            sm.total_reps = r_off + r_incl;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxPulls ? sm.total_reps : kMaxPulls);
+    __syncthreads();
+    if (sm.n_active == 0) return;
+
+    const int tiles_fc1 = static_cast<int>((fc1 + kReduceTileElems - 1) / kReduceTileElems);
+    const int tiles_fc2 = static_cast<int>((fc2 + kReduceTileElems - 1) / kReduceTileElems);
+    const int64_t total_items = static_cast<int64_t>(sm.n_active) * (tiles_fc1 + tiles_fc2);
+    const int64_t first = cta, step = call.ctas_per_rank;
+    const int64_t count = first < total_items ? (total_items - first + step - 1) / step : 0;
+
+    auto replica_ptr = [&](const ReduceItem& it, int r) -> float* {
+        return rk.peer_replica_grad[sm.rep_rank[r]] + static_cast<int64_t>(sm.rep_slot[r]) * total_numel +
+               (it.shard == 0 ? 0 : fc1) + it.offset;
+    };
+    auto master_ptr = [&](const ReduceItem& it) -> float* {
+        const int m = sm.active_master[it.active];
+        const int64_t base = it.shard == 0 ? call.fc1_grad_ptrs[local][m] : call.fc2_grad_ptrs[local][m];
+        return reinterpret_cast<float*>(base) + it.offset;
+    };
+
+    if (!sm.vector_ok) {
+        // element-wise path for sizes / pointers that are not multiples of 16 bytes
+        for (int64_t k = 0; k < count; ++k) {
+            const ReduceItem it = decode_item(first + k * step, sm.n_active, fc1, fc2, tiles_fc1);
+            float* mp = master_ptr(it);
+            const int r0 = sm.rep_start[it.active], r1 = sm.rep_start[it.active + 1];
+            for (int i = tid; i < it.elems; i += blockDim.x) {
+                float acc = mp[i];
+                for (int r = r0; r < r1; ++r) {
+                    if (sm.rep_rank[r] < 0) continue;
+                    float* rp = replica_ptr(it, r);
+                    acc = __fadd_rn(acc, __ldcg(rp + i));
+                    rp[i] = 0.f;
+                }
+                mp[i] = acc;
+            }
+        }
+        __threadfence_system();
+        return;
+    }
+
+    // ---- pipelined path -----------------------------------------------------------------
+    // producer cursor (thread 0): next (item, replica) pair whose load has not been issued
+    int64_t prod_k = 0;
+    int prod_r = -1, prod_r_end = -1;
+    int64_t issued = 0;
+    auto produce_one = [&]() -> bool {  // thread 0 only; false when nothing is left
+        while (true) {
+            if (prod_k >= count) return false;
+            const ReduceItem it = decode_item(first + prod_k * step, sm.n_active, fc1, fc2, tiles_fc1);
+            if (prod_r < 0) {
+                prod_r = sm.rep_start[it.active];
+                prod_r_end = sm.rep_start[it.active + 1];
+            }
+            while (prod_r < prod_r_end && sm.rep_rank[prod_r] < 0) ++prod_r;
+            if (prod_r >= prod_r_end) {
+                ++prod_k;
+                prod_r = -1;
+                continue;
+            }
+            const int s = static_cast<int>(issued % kReduceStages);
+            const uint32_t bytes = static_cast<uint32_t>(it.elems) * 4u;
+            mbar_expect_tx(&bars[s], bytes);
+            bulk_load(smem_raw + s * kReduceTileBytes, replica_ptr(it, prod_r), bytes, &bars[s]);
+            ++issued;
+            ++prod_r;
+            return true;
+        }
+    };
+    if (tid == 0) {
+        for (int s = 0; s < kReduceStages; ++s) {
+            if (!produce_one()) break;
+        }
+    }
+    int64_t consumed = 0;
+    for (int64_t k = 0; k < count; ++k) {
+        const ReduceItem it = decode_item(first + k * step, sm.n_active, fc1, fc2, tiles_fc1);
+        float4* mp = reinterpret_cast<float4*>(master_ptr(it));
+        const int nvec = it.elems >> 2;
+        const bool has0 = tid < nvec, has1 = tid + kReduceThreads < nvec;
+        float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+        if (has0) acc0 = mp[tid];
+        if (has1) acc1 = mp[tid + kReduceThreads];
+        const int r0 = sm.rep_start[it.active], r1 = sm.rep_start[it.active + 1];
+        for (int r = r0; r < r1; ++r) {
+            if (sm.rep_rank[r] < 0) continue;
+            const int s = static_cast<int>(consumed % kReduceStages);
+            if (!mbar_wait(&bars[s], static_cast<uint32_t>((consumed / kReduceStages) & 1), call.timeout_ns)) {
+                sm.error = 1;  // keep the control flow uniform; the result of this tile is void
+            }
+            const float4* stage = reinterpret_cast<const float4*>(smem_raw + s * kReduceTileBytes);
+            if (has0) {
+                const float4 v = stage[tid];
+                acc0.x = __fadd_rn(acc0.x, v.x); acc0.y = __fadd_rn(acc0.y, v.y);
+                acc0.z = __fadd_rn(acc0.z, v.z); acc0.w = __fadd_rn(acc0.w, v.w);
+            }
+            if (has1) {
+                const float4 v = stage[tid + kReduceThreads];
+                acc1.x = __fadd_rn(acc1.x, v.x); acc1.y = __fadd_rn(acc1.y, v.y);
+                acc1.z = __fadd_rn(acc1.z, v.z); acc1.w = __fadd_rn(acc1.w, v.w);
+            }
+            ++consumed;
+            __syncthreads();  // the stage is free again
+            if (tid == 0) {
+                bulk_store(replica_ptr(it, r), zero_tile, static_cast<uint32_t>(it.elems) * 4u);
+                bulk_commit();
+                produce_one();
+            }
+        }
+        if (has0) mp[tid] = acc0;
+        if (has1) mp[tid + kReduceThreads] = acc1;
+    }
+    if (tid == 0) {
+        bulk_wait_all<0>();
+        if (sm.error) {
+            report_error(rk.status, UEP_DEV_TIMEOUT_COPY, static_cast<int>(consumed));
+            for (int64_t j = consumed; j < issued; ++j) {
+                mbar_wait(&bars[j % kReduceStages], static_cast<uint32_t>((j / kReduceStages) & 1), call.timeout_ns);
+            }
+        }
+    }
+    __threadfence_system();
+}
+
+}  // namespace
+
+cudaError_t launch_grad_reduce(const ReduceCall& call, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(kReduceStages + 1) * kReduceTileBytes;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(grad_reduce_kernel),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    count_launch();
+    grad_reduce_kernel<<<call.nlocal * call.ctas_per_rank, kReduceThreads, smem, stream>>>(call);
+    return cudaGetLastError();
+}
+
+}  // namespace uep

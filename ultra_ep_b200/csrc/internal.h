@@ -62,6 +62,7 @@ struct PlanCall {
     uint64_t epoch;
     uint64_t timeout_ns;
     int ctas_per_rank;
+    int withhold_rank;  // test hook: this rank does not publish its flags (-1: none)
 };
 cudaError_t launch_plan(const PlanCall& call, cudaStream_t stream);
 int plan_ctas_per_rank(int input_kind, int max_T, int K_or_L, int nlocal, int num_sms);
@@ -76,6 +77,7 @@ struct SyncCall {
     uint64_t epoch;
     uint64_t timeout_ns;
     int ctas_per_rank;
+    int withhold_rank;  // test hook, as in PlanCall
 };
 cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream);
 int weight_sync_max_ctas_per_rank(int nlocal, int num_sms);
@@ -93,7 +95,42 @@ struct ReduceCall {
 };
 cudaError_t launch_grad_reduce(const ReduceCall& call, cudaStream_t stream);
 
-// stateless reroute / dispatch launchers are reached through the C ABI directly.
+// Reroute launchers. One launch serves every hosted rank (blockIdx.y selects the rank).
+struct DenseFwdArgs {
+    const uint8_t* map;
+    const float* probs;
+    const int32_t *l2p, *lcnts, *rqp;
+    int32_t* scratch;  // [dense tiles][L]
+    uint8_t* out_map;
+    float* out_probs;
+    int T;
+};
+struct DenseBwdArgs {
+    const float* grad_expanded;
+    const uint8_t *map, *expanded_map;
+    const int32_t *l2p, *lcnts;
+    float* grad_probs;
+    int T;
+};
+struct SparseArgs {
+    const void* ids;
+    void* out;
+    const int32_t *l2p, *lcnts, *rqp;
+    int32_t* scratch;  // [sparse tiles][L]
+    int T;
+};
+template <typename A>
+struct Batch {
+    A a[kMaxLocalRanks];
+    int n;
+};
+int64_t dense_scratch_elems(int T, int L);
+int64_t sparse_scratch_elems(int64_t entries, int L);
+cudaError_t launch_dense_forward(const Batch<DenseFwdArgs>& b, int L, int P, int D, int quota_mode, int interleave,
+                                 cudaStream_t stream);
+cudaError_t launch_dense_backward(const Batch<DenseBwdArgs>& b, int L, int P, int D, cudaStream_t stream);
+cudaError_t launch_sparse_reroute(const Batch<SparseArgs>& b, int ids_kind, int K, int L, int D, int interleave,
+                                  cudaStream_t stream);
 
 void set_error(const std::string& msg);
 int fail(int code, const std::string& msg);

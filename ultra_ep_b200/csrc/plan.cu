@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     }
     __threadfence_system();
     __syncthreads();
-    if (tid < N) st_release_sys_u64(rk.peer_gather_flags[tid] + slot * N + me, call.epoch);
+    if (tid < N && me != call.withhold_rank) st_release_sys_u64(rk.peer_gather_flags[tid] + slot * N + me, call.epoch);
 
     // 3. wait for every rank's row (bounded)
     if (tid < N) {

@@ -76,23 +76,35 @@ __device__ __forceinline__ int replica_index(const Router& r, int e, int ordinal
 }
 
 // ----------------------------------------------------------------------------- dense
-__global__ void __launch_bounds__(kRerouteThreads) dense_count_kernel(const uint8_t* __restrict__ map, int T, int L,
-                                                                      int32_t* __restrict__ tile_counts) {
+__global__ void __launch_bounds__(kRerouteThreads) dense_count_kernel(Batch<DenseFwdArgs> batch, int L) {
+    const DenseFwdArgs& a = batch.a[blockIdx.y];
+    const uint8_t* __restrict__ map = a.map;
+    const int T = a.T;
     const int tile = blockIdx.x;
     const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
+    if (r0 >= T) return;
     for (int e = threadIdx.x; e < L; e += blockDim.x) {
         int c = 0;
         for (int t = r0; t < r1; ++t) c += map[static_cast<int64_t>(t) * L + e] ? 1 : 0;
-        tile_counts[static_cast<int64_t>(tile) * L + e] = c;
+        a.scratch[static_cast<int64_t>(tile) * L + e] = c;
     }
 }
 
 __global__ void __launch_bounds__(kRerouteThreads)
-dense_scatter_kernel(const uint8_t* __restrict__ map, const float* __restrict__ probs, const int32_t* __restrict__ l2p,
-                     const int32_t* __restrict__ lcnts, const int32_t* __restrict__ rqp,
-                     const int32_t* __restrict__ tile_counts, uint8_t* __restrict__ out_map,
-                     float* __restrict__ out_probs, int T, int L, int P, int D, int quota_mode, int interleave,
-                     int vec_ok) {
+dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_mode, int interleave) {
+    const DenseFwdArgs& a = batch.a[blockIdx.y];
+    const uint8_t* __restrict__ map = a.map;
+    const float* __restrict__ probs = a.probs;
+    const int32_t* __restrict__ l2p = a.l2p;
+    const int32_t* __restrict__ lcnts = a.lcnts;
+    const int32_t* __restrict__ rqp = a.rqp;
+    const int32_t* __restrict__ tile_counts = a.scratch;
+    uint8_t* __restrict__ out_map = a.out_map;
+    float* __restrict__ out_probs = a.out_probs;
+    const int T = a.T;
+    if (static_cast<int>(blockIdx.x) * kDenseTileRows >= T) return;
+    const int vec_ok = ((P & 3) == 0) && ((reinterpret_cast<uintptr_t>(out_probs) & 15u) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(out_map) & 3u) == 0);
     extern __shared__ __align__(128) char smem_raw[];
     // layout: inv[P] int32 | choice[rows][L] uint8
     int32_t* inv = reinterpret_cast<int32_t*>(smem_raw);
@@ -167,11 +179,15 @@ dense_scatter_kernel(const uint8_t* __restrict__ map, const float* __restrict__ 
     }
 }
 
-__global__ void __launch_bounds__(kRerouteThreads)
-dense_backward_kernel(const float* __restrict__ grad_expanded, const uint8_t* __restrict__ map,
-                      const uint8_t* __restrict__ expanded_map, const int32_t* __restrict__ l2p,
-                      const int32_t* __restrict__ lcnts, float* __restrict__ grad_probs, int64_t total, int L, int P,
-                      int D) {
+__global__ void __launch_bounds__(kRerouteThreads) dense_backward_kernel(Batch<DenseBwdArgs> batch, int L, int P, int D) {
+    const DenseBwdArgs& a = batch.a[blockIdx.y];
+    const float* __restrict__ grad_expanded = a.grad_expanded;
+    const uint8_t* __restrict__ map = a.map;
+    const uint8_t* __restrict__ expanded_map = a.expanded_map;
+    const int32_t* __restrict__ l2p = a.l2p;
+    const int32_t* __restrict__ lcnts = a.lcnts;
+    float* __restrict__ grad_probs = a.grad_probs;
+    const int64_t total = static_cast<int64_t>(a.T) * L;
     for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
          idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         float g = 0.f;
@@ -271,12 +287,38 @@ __device__ void tile_ordinals(const IdT* keys, int64_t n, int nb_valid, bool tai
 }
 
 template <typename IdT>
-__global__ void __launch_bounds__(kRerouteThreads)
-sparse_reroute_kernel(const IdT* ids, IdT* out, int64_t n, int L,
-                      const int32_t* __restrict__ l2p, const int32_t* __restrict__ lcnts,
-                      const int32_t* __restrict__ rqp, int D, int interleave,
-                      const int32_t* __restrict__ tile_counts) {
+__global__ void __launch_bounds__(kRerouteThreads) sparse_count_kernel(Batch<SparseArgs> batch, int K, int L) {
     extern __shared__ __align__(128) char smem_raw[];
+    const SparseArgs& a = batch.a[blockIdx.y];
+    const IdT* keys = static_cast<const IdT*>(a.ids);
+    const int64_t n = static_cast<int64_t>(a.T) * K;
+    const int64_t begin = static_cast<int64_t>(blockIdx.x) * kSparseTileEntries;
+    if (begin >= n) return;
+    int32_t* hist = reinterpret_cast<int32_t*>(smem_raw);
+    for (int i = threadIdx.x; i < L; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const int64_t end = min(begin + kSparseTileEntries, n);
+    for (int64_t i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const int b = key_bucket<IdT>(keys[i], L, false);
+        if (b >= 0) atomicAdd(hist + b, 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < L; i += blockDim.x) a.scratch[static_cast<int64_t>(blockIdx.x) * L + i] = hist[i];
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kRerouteThreads)
+sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interleave) {
+    extern __shared__ __align__(128) char smem_raw[];
+    const SparseArgs& a = batch.a[blockIdx.y];
+    const IdT* ids = static_cast<const IdT*>(a.ids);
+    IdT* out = static_cast<IdT*>(a.out);
+    const int32_t* __restrict__ l2p = a.l2p;
+    const int32_t* __restrict__ lcnts = a.lcnts;
+    const int32_t* __restrict__ rqp = a.rqp;
+    const int32_t* __restrict__ tile_counts = a.scratch;
+    const int64_t n = static_cast<int64_t>(a.T) * K;
+    if (static_cast<int64_t>(blockIdx.x) * kSparseTileEntries >= n) return;
     // layout: base[L] | routers[L] | warp_base[nwarps][L]
     int32_t* base = reinterpret_cast<int32_t*>(smem_raw);
     Router* routers = reinterpret_cast<Router*>(base + L);
@@ -289,8 +331,8 @@ sparse_reroute_kernel(const IdT* ids, IdT* out, int64_t n, int L,
         routers[e] = make_router(e, lcnts, rqp, D, true, interleave != 0);
     }
     __syncthreads();
-    // ids may alias out: every entry is read (three times) and written by the same lane, the
-    // write comes last, and tiles do not overlap.
+    // ids may alias out: every entry is read and written by the same lane, the write comes
+    // last, and tiles do not overlap.
     tile_ordinals<IdT>(ids, n, L, false, base, warp_base, [&](int64_t i, int b, int ordinal) {
         if (b < 0) {
             out[i] = ids[i];
@@ -453,27 +495,66 @@ cudaError_t ensure_smem_attr(const void* fn, size_t bytes) {
 int dense_tiles(int T) { return (T + kDenseTileRows - 1) / kDenseTileRows; }
 int64_t sparse_tiles(int64_t n) { return (n + kSparseTileEntries - 1) / kSparseTileEntries; }
 
-template <typename IdT>
-int sparse_reroute_impl(const IdT* ids, IdT* out, int T, int K, int L, const int32_t* l2p, const int32_t* lcnts,
-                        const int32_t* rqp, int D, int interleave, int32_t* scratch, cudaStream_t stream) {
-    if (T < 0 || K < 0 || L <= 0 || D < 1) return fail(UEP_ERR_INVALID, "sparse_reroute: bad sizes");
-    const int64_t n = static_cast<int64_t>(T) * K;
-    if (n == 0) return UEP_OK;
-    if (ids == nullptr || out == nullptr || scratch == nullptr) return fail(UEP_ERR_INVALID, "sparse_reroute: null pointer");
-    const int tiles = static_cast<int>(sparse_tiles(n));
-    const size_t smem1 = sizeof(int32_t) * L;
-    const size_t smem2 = sizeof(int32_t) * L + sizeof(Router) * L + sizeof(int32_t) * (kRerouteThreads / 32) * L;
-    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(key_count_kernel<IdT>), smem1));
-    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(sparse_reroute_kernel<IdT>), smem2));
+}  // namespace
+
+int64_t dense_scratch_elems(int T, int L) { return static_cast<int64_t>(dense_tiles(T)) * L + 4; }
+int64_t sparse_scratch_elems(int64_t entries, int L) { return sparse_tiles(entries) * L + 4; }
+
+cudaError_t launch_dense_forward(const Batch<DenseFwdArgs>& b, int L, int P, int D, int quota_mode, int interleave,
+                                 cudaStream_t stream) {
+    int max_T = 0;
+    for (int i = 0; i < b.n; ++i) max_T = b.a[i].T > max_T ? b.a[i].T : max_T;
+    if (max_T == 0) return cudaSuccess;
+    const dim3 grid(dense_tiles(max_T), b.n);
+    const size_t smem = sizeof(int32_t) * P + static_cast<size_t>(kDenseTileRows) * L + 16;
+    cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(dense_scatter_kernel), smem);
+    if (e != cudaSuccess) return e;
     count_launch(2);
-    key_count_kernel<IdT><<<tiles, kRerouteThreads, smem1, stream>>>(ids, n, L, 0, scratch);
-    sparse_reroute_kernel<IdT><<<tiles, kRerouteThreads, smem2, stream>>>(ids, out, n, L, l2p, lcnts, rqp, D,
-                                                                         interleave, scratch);
-    UEP_CUDA_TRY(cudaGetLastError());
-    return UEP_OK;
+    dense_count_kernel<<<grid, kRerouteThreads, 0, stream>>>(b, L);
+    dense_scatter_kernel<<<grid, kRerouteThreads, smem, stream>>>(b, L, P, D, quota_mode, interleave);
+    return cudaGetLastError();
 }
 
-}  // namespace
+cudaError_t launch_dense_backward(const Batch<DenseBwdArgs>& b, int L, int P, int D, cudaStream_t stream) {
+    int max_T = 0;
+    for (int i = 0; i < b.n; ++i) max_T = b.a[i].T > max_T ? b.a[i].T : max_T;
+    if (max_T == 0) return cudaSuccess;
+    int64_t blocks = (static_cast<int64_t>(max_T) * L + kRerouteThreads - 1) / kRerouteThreads;
+    const int64_t cap = (148 * 16) / b.n > 1 ? (148 * 16) / b.n : 1;
+    if (blocks > cap) blocks = cap;
+    count_launch();
+    dense_backward_kernel<<<dim3(static_cast<unsigned>(blocks), b.n), kRerouteThreads, 0, stream>>>(b, L, P, D);
+    return cudaGetLastError();
+}
+
+template <typename IdT>
+static cudaError_t launch_sparse_typed(const Batch<SparseArgs>& b, int K, int L, int D, int interleave,
+                                       cudaStream_t stream) {
+    int64_t max_n = 0;
+    for (int i = 0; i < b.n; ++i) {
+        const int64_t n = static_cast<int64_t>(b.a[i].T) * K;
+        max_n = n > max_n ? n : max_n;
+    }
+    if (max_n == 0) return cudaSuccess;
+    const dim3 grid(static_cast<unsigned>(sparse_tiles(max_n)), b.n);
+    const size_t smem1 = sizeof(int32_t) * L;
+    const size_t smem2 = sizeof(int32_t) * L + sizeof(Router) * L + sizeof(int32_t) * (kRerouteThreads / 32) * L;
+    cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(sparse_count_kernel<IdT>), smem1);
+    if (e != cudaSuccess) return e;
+    e = ensure_smem_attr(reinterpret_cast<const void*>(sparse_reroute_kernel<IdT>), smem2);
+    if (e != cudaSuccess) return e;
+    count_launch(2);
+    sparse_count_kernel<IdT><<<grid, kRerouteThreads, smem1, stream>>>(b, K, L);
+    sparse_reroute_kernel<IdT><<<grid, kRerouteThreads, smem2, stream>>>(b, K, L, D, interleave);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sparse_reroute(const Batch<SparseArgs>& b, int ids_kind, int K, int L, int D, int interleave,
+                                  cudaStream_t stream) {
+    if (ids_kind == 2) return launch_sparse_typed<long long>(b, K, L, D, interleave, stream);
+    return launch_sparse_typed<int32_t>(b, K, L, D, interleave, stream);
+}
+
 }  // namespace uep
 
 using namespace uep;
@@ -481,8 +562,8 @@ using namespace uep;
 extern "C" {
 
 int64_t uep_reroute_scratch_elems(int64_t T, int K_or_0, int L) {
-    if (K_or_0 <= 0) return static_cast<int64_t>(dense_tiles(static_cast<int>(T))) * L + 4;
-    return sparse_tiles(T * K_or_0) * L + 4;
+    if (K_or_0 <= 0) return dense_scratch_elems(static_cast<int>(T), L);
+    return sparse_scratch_elems(T * K_or_0, L);
 }
 
 int uep_dense_reroute_forward(const uint8_t* routing_map, const float* probs, const int32_t* l2p,
@@ -495,18 +576,10 @@ int uep_dense_reroute_forward(const uint8_t* routing_map, const float* probs, co
         (quota_mode && !rank_quota_prefix))
         return fail(UEP_ERR_INVALID, "dense_reroute_forward: null pointer");
     if (D > 255) return fail(UEP_ERR_INVALID, "dense_reroute_forward: more than 255 replicas per expert");
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    const int tiles = dense_tiles(T);
-    const int vec_ok = ((P & 3) == 0) && ((reinterpret_cast<uintptr_t>(expanded_probs) & 15u) == 0) &&
-                       ((reinterpret_cast<uintptr_t>(expanded_map) & 3u) == 0);
-    const size_t smem = sizeof(int32_t) * P + static_cast<size_t>(kDenseTileRows) * L + 16;
-    UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(dense_scatter_kernel), smem));
-    count_launch(2);
-    dense_count_kernel<<<tiles, kRerouteThreads, 0, stream>>>(routing_map, T, L, scratch);
-    dense_scatter_kernel<<<tiles, kRerouteThreads, smem, stream>>>(routing_map, probs, l2p, lcnts, rank_quota_prefix,
-                                                                   scratch, expanded_map, expanded_probs, T, L, P, D,
-                                                                   quota_mode, interleave, vec_ok);
-    UEP_CUDA_TRY(cudaGetLastError());
+    Batch<DenseFwdArgs> b{};
+    b.n = 1;
+    b.a[0] = DenseFwdArgs{routing_map, probs, l2p, lcnts, rank_quota_prefix, scratch, expanded_map, expanded_probs, T};
+    UEP_CUDA_TRY(launch_dense_forward(b, L, P, D, quota_mode, interleave, static_cast<cudaStream_t>(stream_)));
     return UEP_OK;
 }
 
@@ -517,28 +590,35 @@ int uep_dense_reroute_backward(const float* grad_expanded, const uint8_t* routin
     if (T == 0) return UEP_OK;
     if (!grad_expanded || !routing_map || !expanded_map || !l2p || !lcnts || !grad_probs)
         return fail(UEP_ERR_INVALID, "dense_reroute_backward: null pointer");
-    const int64_t total = static_cast<int64_t>(T) * L;
-    int64_t blocks = (total + kRerouteThreads - 1) / kRerouteThreads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    count_launch();
-    dense_backward_kernel<<<static_cast<int>(blocks), kRerouteThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
-        grad_expanded, routing_map, expanded_map, l2p, lcnts, grad_probs, total, L, P, D);
-    UEP_CUDA_TRY(cudaGetLastError());
+    Batch<DenseBwdArgs> b{};
+    b.n = 1;
+    b.a[0] = DenseBwdArgs{grad_expanded, routing_map, expanded_map, l2p, lcnts, grad_probs, T};
+    UEP_CUDA_TRY(launch_dense_backward(b, L, P, D, static_cast<cudaStream_t>(stream_)));
+    return UEP_OK;
+}
+
+static int sparse_common(int kind, const void* ids, void* out, int T, int K, int L, const int32_t* l2p,
+                         const int32_t* lcnts, const int32_t* rqp, int D, int interleave, int32_t* scratch,
+                         void* stream_) {
+    if (T < 0 || K < 0 || L <= 0 || D < 1) return fail(UEP_ERR_INVALID, "sparse_reroute: bad sizes");
+    if (static_cast<int64_t>(T) * K == 0) return UEP_OK;
+    if (!ids || !out || !scratch || !l2p || !lcnts || !rqp) return fail(UEP_ERR_INVALID, "sparse_reroute: null pointer");
+    Batch<SparseArgs> b{};
+    b.n = 1;
+    b.a[0] = SparseArgs{ids, out, l2p, lcnts, rqp, scratch, T};
+    UEP_CUDA_TRY(launch_sparse_reroute(b, kind, K, L, D, interleave, static_cast<cudaStream_t>(stream_)));
     return UEP_OK;
 }
 
 int uep_sparse_reroute_i32(const int32_t* ids, int32_t* out, int T, int K, int L, const int32_t* l2p,
                            const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
                            int32_t* scratch, void* stream) {
-    return sparse_reroute_impl<int32_t>(ids, out, T, K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch,
-                                        static_cast<cudaStream_t>(stream));
+    return sparse_common(1, ids, out, T, K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch, stream);
 }
 int uep_sparse_reroute_i64(const int64_t* ids, int64_t* out, int T, int K, int L, const int32_t* l2p,
                            const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
                            int32_t* scratch, void* stream) {
-    return sparse_reroute_impl<long long>(reinterpret_cast<const long long*>(ids), reinterpret_cast<long long*>(out), T,
-                                          K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch,
-                                          static_cast<cudaStream_t>(stream));
+    return sparse_common(2, ids, out, T, K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch, stream);
 }
 
 int64_t uep_dispatch_scratch_elems(int64_t num_entries, int P) { return sparse_tiles(num_entries) * (P + 1) + 4; }

@@ -264,7 +264,9 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     __syncthreads();
     if (!sm.is_last) return;
     for (int p = tid; p < N; p += blockDim.x) {
-        if (sm.send_mask[p >> 5] & (1u << (p & 31))) st_release_sys_u64(rk.peer_sync_flags[p] + me, call.epoch);
+        if ((sm.send_mask[p >> 5] & (1u << (p & 31))) && me != call.withhold_rank) {
+            st_release_sys_u64(rk.peer_sync_flags[p] + me, call.epoch);
+        }
     }
     for (int p = tid; p < N; p += blockDim.x) {
         if (sm.recv_mask[p >> 5] & (1u << (p & 31))) {
