@@ -1,0 +1,133 @@
+"""CPU-only tests: the library loads and exports every declared symbol, the configuration layer
+keeps the reference's variable names / defaults / validation, virtual-layer arithmetic, and the
+two-rank bootstrap (gloo) that carries the arena handles between processes."""
+
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(native_lib):
+    from ultra_ep_b200 import capi
+
+    assert capi.MISSING == []
+    header = open(os.path.join(ROOT, "include", "uep_b200.h")).read()
+    declared = set(re.findall(r"\b(uep_[a-z0-9_]+)\s*\(", header))
+    declared -= {"uep_status"}
+    for name in sorted(declared):
+        assert hasattr(native_lib, name), f"{name} is declared in include/uep_b200.h but not exported"
+        assert name in capi.SIGNATURES, f"{name} has no ctypes signature in ultra_ep_b200/capi.py"
+    assert native_lib.uep_version().startswith(b"uep_b200")
+
+
+def test_no_compute_without_gpu_but_clean_errors(native_lib):
+    """Argument validation happens on the host and never needs a device."""
+    import ctypes as C
+
+    from ultra_ep_b200 import capi
+
+    prm = capi.SolverParams.defaults()
+    assert native_lib.uep_solve_placement(None, None, None, None, None, None, None, None, 8, 8, 8, 2, 8, C.byref(prm),
+                                          0, None, None) == -1
+    assert b"null argument" in native_lib.uep_last_error()
+    assert native_lib.uep_manager_create(None, None) == -1
+    assert native_lib.uep_reroute_scratch_elems(8192, 8, 128) == 32 * 128 + 4
+    assert native_lib.uep_reroute_scratch_elems(8192, 0, 128) == 128 * 128 + 4
+
+
+def test_tuning_defaults_and_validation(monkeypatch):
+    from ultra_ep_b200.config import load_tuning_from_env
+
+    for k in list(os.environ):
+        if k.startswith("ULTRA_EP_"):
+            monkeypatch.delenv(k)
+    t = load_tuning_from_env()
+    assert (t.balance_threshold, t.quota_locality_aware, t.quota_min_tokens_per_replica) == (1.0, True, 1024)
+    assert (t.quota_allow_zero_master_quota, t.quota_oracle_eps, t.quota_kernel_stage) == (False, 0.01, 1)
+    assert (t.quota_reroute_interleave, t.grad_reduce_num_sms, t.grad_reduce_deterministic) == (True, 42, True)
+    assert (t.weight_sync_plan_mode, t.weight_sync_plan_mode_id) == ("adaptive", 1)
+    assert (t.weight_sync_relay_min_replicas, t.weight_sync_relay_max_relays, t.weight_sync_relay_min_fanout_gain) == (4, 8, 2)
+    monkeypatch.setenv("ULTRA_EP_GRAD_REDUCE_NUM_SMS", "41")
+    with pytest.raises(ValueError):
+        load_tuning_from_env()
+    monkeypatch.setenv("ULTRA_EP_GRAD_REDUCE_NUM_SMS", "64")
+    monkeypatch.setenv("ULTRA_EP_WEIGHT_SYNC_PLAN_MODE", "Force_Relay")
+    monkeypatch.setenv("ULTRA_EP_QUOTA_LOCALITY_AWARE", "off")
+    monkeypatch.setenv("ULTRA_EP_QUOTA_ORACLE_EPS", " 0.05 ")
+    t = load_tuning_from_env()
+    assert t.grad_reduce_num_sms == 64 and t.weight_sync_plan_mode_id == 2 and t.quota_locality_aware is False
+    assert t.quota_oracle_eps == 0.05
+    monkeypatch.setenv("ULTRA_EP_QUOTA_KERNEL_STAGE", "2")
+    with pytest.raises(ValueError):
+        load_tuning_from_env()
+    monkeypatch.setenv("ULTRA_EP_QUOTA_KERNEL_STAGE", "1")
+    monkeypatch.setenv("ULTRA_EP_QUOTA_REROUTE_INTERLEAVE", "maybe")
+    with pytest.raises(ValueError):
+        load_tuning_from_env()
+
+
+def test_microbatch_slot_arithmetic():
+    from ultra_ep_b200.manager import Manager
+
+    m = Manager.__new__(Manager)
+    m.max_microbatches = 4
+    m.real_num_alloc_layers = 5
+    m._mb_counters = [0] * 5
+    assert [m.allocate_microbatch_slot(2) for _ in range(6)] == [8, 9, 10, 11, 8, 9]
+    assert m.allocate_microbatch_slot(0) == 0
+    assert m._real_layer_id(11) == 2
+    with pytest.raises(AssertionError):
+        m.allocate_microbatch_slot(5)
+
+
+WORKER = r'''
+import os, sys
+sys.path.insert(0, os.environ["UEP_ROOT"])
+import torch.distributed as dist
+dist.init_process_group("gloo")
+from ultra_ep_b200 import runtime
+from ultra_ep_b200.native import load
+C = load()
+captured = {}
+orig = C.set_handle_exchange
+def spy(fn):
+    captured["fn"] = fn
+    orig(fn)
+C.set_handle_exchange = spy
+peers = runtime.init_runtime(dist.group.WORLD)
+assert peers == 2 and C.is_runtime_initialized()
+assert runtime.init_runtime(dist.group.WORLD) == 2           # idempotent
+rank = dist.get_rank()
+blob = bytes([rank]) * 64
+parts = captured["fn"](blob)
+assert [p[0] for p in parts] == [0, 1] and all(len(p) == 64 for p in parts)
+# a Manager cannot be built without a CUDA device: the error must be loud, not a fallback
+try:
+    C.Manager(1, 2, 1, 16, 16, 2, 1, 0, 0, 4, True, True)
+    raise SystemExit("Manager construction without a GPU must fail")
+except RuntimeError as e:
+    assert "CUDA" in str(e) or "cuda" in str(e), str(e)
+runtime.shutdown_runtime()
+assert not C.is_runtime_initialized()
+dist.barrier()
+open(os.path.join(os.environ["UEP_OUT"], f"ok{rank}"), "w").write("ok")
+'''
+
+
+def test_two_rank_bootstrap_over_gloo(tmp_path, native_lib):
+    from ultra_ep_b200 import build
+
+    build.build_ext()
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, UEP_ROOT=ROOT, UEP_OUT=str(tmp_path), CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+         "--master-port", "29631", str(script)], env=env, capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()

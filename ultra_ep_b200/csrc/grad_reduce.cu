@@ -33,10 +33,9 @@ constexpr int kMaxPulls = kMaxExportsPerDomain;
 
 struct ReduceShared {
     int n_active, total_reps, vector_ok, error;
-    short active_master[kMaxExpertsPerDomain];
     short rep_start[kMaxExpertsPerDomain + 1];
-    short rep_rank[kMaxPulls];
-    short rep_slot[kMaxPulls];
+    float* rep_base[kMaxPulls];                    // replica slot base in the peer's grad buffer (null: skip)
+    float* master[kMaxExpertsPerDomain][2];        // [n_active][fc1, fc2] master gradient base
 };
 
 struct ReduceItem {
@@ -49,8 +48,9 @@ struct ReduceItem {
 __device__ __forceinline__ ReduceItem decode_item(int64_t idx, int n_active, int64_t fc1_numel, int64_t fc2_numel,
                                                   int tiles_fc1) {
     ReduceItem it;
-    it.active = static_cast<int>(idx % n_active);
-    const int tile = static_cast<int>(idx / n_active);
+    const int idx32 = static_cast<int>(idx);
+    it.active = idx32 % n_active;
+    const int tile = idx32 / n_active;
     it.shard = tile < tiles_fc1 ? 0 : 1;
     const int t = it.shard == 0 ? tile : tile - tiles_fc1;
     it.offset = static_cast<int64_t>(t) * kReduceTileElems;
@@ -64,14 +64,11 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
     __shared__ ReduceShared sm;
     __shared__ __align__(8) uint64_t bars[kReduceStages];
 
-    const int local = blockIdx.x / call.ctas_per_rank;
-    const int cta = blockIdx.x % call.ctas_per_rank;
-    const RankDev& rk = *call.rank[local];
-    const PlanPtrs& plan = call.plan[local];
-    const int me = rk.my_rank, M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N;
+    const int M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N, nlocal = call.nlocal;
     const int tid = threadIdx.x;
     const int64_t fc1 = call.fc1_numel, fc2 = call.fc2_numel, total_numel = fc1 + fc2;
     float* zero_tile = reinterpret_cast<float*>(smem_raw + kReduceStages * kReduceTileBytes);
+    DeviceStatus* status0 = call.rank[0]->status;
 
     if (tid == 0) {
         sm.n_active = 0;
@@ -85,11 +82,18 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
     fence_proxy_async_smem();
     __syncthreads();
 
-    // pull list: masters of this rank with replicas, and where each replica lives
-    for (int m0 = 0; m0 < M; m0 += blockDim.x) {
-        const int m = m0 + tid;
+    // pull list: masters of the hosted ranks with replicas, and where each replica lives.
+    // Hosted ranks pool their tiles over all CTAs of the launch.
+    const int total_masters = nlocal * M;
+    for (int g0 = 0; g0 < total_masters; g0 += blockDim.x) {
+        const int gm = g0 + tid;
+        const int lr = gm < total_masters ? gm / M : 0;
+        const int m = gm < total_masters ? gm % M : 0;
+        const RankDev& rk = *call.rank[lr];
+        const PlanPtrs& plan = call.plan[lr];
+        const int me = rk.my_rank;
         int reps = 0;
-        if (m < M) {
+        if (gm < total_masters) {
             reps = plan.lcnts[me * M + m] - 1;
             reps = reps < 0 ? 0 : (reps > D - 1 ? D - 1 : reps);
         }
@@ -118,24 +122,23 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
         if (act) {
             const int ai = a_off + a_incl - 1;
             const int rs = r_off + r_incl - reps;
-            sm.active_master[ai] = static_cast<short>(m);
             sm.rep_start[ai] = static_cast<short>(rs);
             const int l = me * M + m;
             for (int j = 0; j < reps && rs + j < kMaxPulls; ++j) {
                 const int phys = plan.l2p[static_cast<int64_t>(l) * D + 1 + j];
-                int prank = phys / Lp, pslot = phys % Lp - M;
+                const int prank = phys / Lp, pslot = phys % Lp - M;
                 if (phys < 0 || prank >= N || pslot < 0 || pslot >= R) {
                     report_error(rk.status, UEP_DEV_BAD_PLAN, l);
-                    prank = -1;
-                    pslot = 0;
+                    sm.rep_base[rs + j] = nullptr;
+                } else {
+                    sm.rep_base[rs + j] = rk.peer_replica_grad[prank] + static_cast<int64_t>(pslot) * total_numel;
                 }
-                sm.rep_rank[rs + j] = static_cast<short>(prank);
-                sm.rep_slot[rs + j] = static_cast<short>(pslot);
             }
-            if ((static_cast<uintptr_t>(call.fc1_grad_ptrs[local][m]) & 15u) ||
-                (static_cast<uintptr_t>(call.fc2_grad_ptrs[local][m]) & 15u)) {
-                atomicAnd(&sm.vector_ok, 0);
-            }
+            const uintptr_t p1 = static_cast<uintptr_t>(call.fc1_grad_ptrs[lr][m]);
+            const uintptr_t p2 = static_cast<uintptr_t>(call.fc2_grad_ptrs[lr][m]);
+            sm.master[ai][0] = reinterpret_cast<float*>(p1);
+            sm.master[ai][1] = reinterpret_cast<float*>(p2);
+            if ((p1 & 15u) || (p2 & 15u)) atomicAnd(&sm.vector_ok, 0);
         }
         __syncthreads();
         if (tid == blockDim.x - 1) {
@@ -151,18 +154,13 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
     const int tiles_fc1 = static_cast<int>((fc1 + kReduceTileElems - 1) / kReduceTileElems);
     const int tiles_fc2 = static_cast<int>((fc2 + kReduceTileElems - 1) / kReduceTileElems);
     const int64_t total_items = static_cast<int64_t>(sm.n_active) * (tiles_fc1 + tiles_fc2);
-    const int64_t first = cta, step = call.ctas_per_rank;
+    const int64_t first = blockIdx.x, step = gridDim.x;
     const int64_t count = first < total_items ? (total_items - first + step - 1) / step : 0;
 
     auto replica_ptr = [&](const ReduceItem& it, int r) -> float* {
-        return rk.peer_replica_grad[sm.rep_rank[r]] + static_cast<int64_t>(sm.rep_slot[r]) * total_numel +
-               (it.shard == 0 ? 0 : fc1) + it.offset;
+        return sm.rep_base[r] + (it.shard == 0 ? 0 : fc1) + it.offset;
     };
-    auto master_ptr = [&](const ReduceItem& it) -> float* {
-        const int m = sm.active_master[it.active];
-        const int64_t base = it.shard == 0 ? call.fc1_grad_ptrs[local][m] : call.fc2_grad_ptrs[local][m];
-        return reinterpret_cast<float*>(base) + it.offset;
-    };
+    auto master_ptr = [&](const ReduceItem& it) -> float* { return sm.master[it.active][it.shard] + it.offset; };
 
     if (!sm.vector_ok) {
         // element-wise path for sizes / pointers that are not multiples of 16 bytes
@@ -173,7 +171,7 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
             for (int i = tid; i < it.elems; i += blockDim.x) {
                 float acc = mp[i];
                 for (int r = r0; r < r1; ++r) {
-                    if (sm.rep_rank[r] < 0) continue;
+                    if (sm.rep_base[r] == nullptr) continue;
                     float* rp = replica_ptr(it, r);
                     acc = __fadd_rn(acc, __ldcg(rp + i));
                     rp[i] = 0.f;
@@ -198,7 +196,7 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
                 prod_r = sm.rep_start[it.active];
                 prod_r_end = sm.rep_start[it.active + 1];
             }
-            while (prod_r < prod_r_end && sm.rep_rank[prod_r] < 0) ++prod_r;
+            while (prod_r < prod_r_end && sm.rep_base[prod_r] == nullptr) ++prod_r;
             if (prod_r >= prod_r_end) {
                 ++prod_k;
                 prod_r = -1;
@@ -229,7 +227,7 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
         if (has1) acc1 = mp[tid + kReduceThreads];
         const int r0 = sm.rep_start[it.active], r1 = sm.rep_start[it.active + 1];
         for (int r = r0; r < r1; ++r) {
-            if (sm.rep_rank[r] < 0) continue;
+            if (sm.rep_base[r] == nullptr) continue;
             const int s = static_cast<int>(consumed % kReduceStages);
             if (!mbar_wait(&bars[s], static_cast<uint32_t>((consumed / kReduceStages) & 1), call.timeout_ns)) {
                 sm.error = 1;  // keep the control flow uniform; the result of this tile is void
@@ -259,7 +257,7 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
     if (tid == 0) {
         bulk_wait_all<0>();
         if (sm.error) {
-            report_error(rk.status, UEP_DEV_TIMEOUT_COPY, static_cast<int>(consumed));
+            report_error(status0, UEP_DEV_TIMEOUT_COPY, static_cast<int>(consumed));
             for (int64_t j = consumed; j < issued; ++j) {
                 mbar_wait(&bars[j % kReduceStages], static_cast<uint32_t>((j / kReduceStages) & 1), call.timeout_ns);
             }

@@ -11,10 +11,12 @@
 //     read from local HBM once (cp.async.bulk global->shared, mbarrier) and stored to each
 //     destination slot (cp.async.bulk shared->global, peer memory over NVLink); loads run
 //     up to three tiles ahead of the stores;
-//   * tiles are interleaved over masters so that concurrent CTAs feed different peers;
+//   * tiles are interleaved over masters so that concurrent CTAs feed different peers; when
+//     several ranks are hosted on one device their tiles form one pool shared by all CTAs;
 //   * the CTA that finishes last publishes "rank r has delivered epoch e" to the ranks it
 //     sent to (system-scope release) and waits, bounded, for the same word from the ranks
 //     that send to it. When the kernel ends, this rank's replica slots are complete.
+//     No CTA waits for another CTA of the same launch.
 // Pointers or sizes that are not multiples of 16 bytes take a plain vector/byte copy path.
 
 #include "internal.h"
@@ -29,17 +31,19 @@ constexpr int kSyncStages = 4;
 constexpr int kMaxSends = kMaxExportsPerDomain;  // replicas of one rank's masters never exceed G*R <= 512
 
 struct SyncShared {
-    int n_active;          // masters of this rank that have replicas
+    int n_active;          // masters (of all hosted ranks) that have replicas
     int total_reps;        // sum of their replica counts
     int all_aligned;       // every source pointer 16-byte aligned
     int is_last;
-    unsigned send_mask[3]; // ranks this rank sends to
-    unsigned recv_mask[3]; // ranks that send to this rank
+    unsigned send_mask[kMaxLocalRanks][3];  // per hosted rank: ranks it sends to
+    unsigned recv_mask[kMaxLocalRanks][3];  // per hosted rank: ranks that send to it
     int timeout_peer;
-    short active_master[kMaxExpertsPerDomain];  // [n_active] local master index
-    short rep_start[kMaxExpertsPerDomain + 1];  // [n_active+1] offsets into rep_*
-    short rep_rank[kMaxSends];
-    short rep_slot[kMaxSends];
+    short rep_start[kMaxExpertsPerDomain + 1];  // [n_active+1] offsets into dst_*
+    // Addresses are resolved once per CTA: the issuing thread must not chase pointers
+    // through global memory for every 32 KiB tile.
+    const uint8_t* src[kMaxExpertsPerDomain][4];  // [n_active][shard] master shard base
+    uint8_t* dst_weight[kMaxSends];               // replica slot base in the peer's weight buffer (null: skip)
+    uint8_t* dst_scale[kMaxSends];                // replica slot base in the peer's scale buffer
 };
 
 struct TileRef {
@@ -51,8 +55,9 @@ struct TileRef {
 
 __device__ __forceinline__ TileRef decode_tile(int64_t idx, int n_active, const ShardLayout& sh, const int* shard_tiles) {
     TileRef t;
-    t.active = static_cast<int>(idx % n_active);
-    int tile = static_cast<int>(idx / n_active);
+    const int idx32 = static_cast<int>(idx);  // tile counts fit 32 bits (checked on the host side by construction)
+    t.active = idx32 % n_active;
+    int tile = idx32 / n_active;
     t.shard = 0;
     while (t.shard < sh.num_shards - 1 && tile >= shard_tiles[t.shard]) {
         tile -= shard_tiles[t.shard];
@@ -64,9 +69,8 @@ __device__ __forceinline__ TileRef decode_tile(int64_t idx, int n_active, const 
     return t;
 }
 
-__device__ __forceinline__ uint8_t* dest_addr(const RankDev& rk, const ShardLayout& sh, int shard, int rank, int slot) {
-    if (shard < 2) return rk.peer_replica_weight[rank] + static_cast<int64_t>(slot) * sh.weight_slot_stride + sh.slot_offset[shard];
-    return rk.peer_replica_scale[rank] + static_cast<int64_t>(slot) * sh.scale_slot_stride + sh.slot_offset[shard];
+__device__ __forceinline__ uint8_t* dest_addr(const SyncShared& sm, const ShardLayout& sh, int shard, int rep) {
+    return (shard < 2 ? sm.dst_weight[rep] : sm.dst_scale[rep]) + sh.slot_offset[shard];
 }
 
 __device__ void copy_plain(const uint8_t* src, uint8_t* dst, int bytes) {
@@ -88,32 +92,37 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     __shared__ __align__(8) uint64_t bars[kSyncStages];
     __shared__ int shard_tiles[4];
 
-    const int local = blockIdx.x / call.ctas_per_rank;
-    const int cta = blockIdx.x % call.ctas_per_rank;
-    const RankDev& rk = *call.rank[local];
-    const PlanPtrs& plan = call.plan[local];
     const ShardLayout& sh = call.shards;
-    const int me = rk.my_rank, M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N;
+    const int M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N, nlocal = call.nlocal;
     const int tid = threadIdx.x;
 
-    // ---- setup: send list of this rank from the plan ---------------------------------
+    // ---- setup: send list of the hosted ranks from their plans ---------------------------
     if (tid == 0) {
         sm.n_active = 0;
         sm.total_reps = 0;
         sm.all_aligned = 1;
         sm.is_last = 0;
         sm.timeout_peer = -1;
-        for (int w = 0; w < 3; ++w) sm.send_mask[w] = sm.recv_mask[w] = 0;
         for (int s = 0; s < 4; ++s) shard_tiles[s] = s < sh.num_shards ? static_cast<int>((sh.bytes[s] + kSyncTile - 1) / kSyncTile) : 0;
         for (int s = 0; s < kSyncStages; ++s) mbar_init(&bars[s], 1);
         fence_mbar_init();
     }
+    for (int i = tid; i < kMaxLocalRanks * 3; i += blockDim.x) {
+        sm.send_mask[i / 3][i % 3] = 0;
+        sm.recv_mask[i / 3][i % 3] = 0;
+    }
     __syncthreads();
-    // blocked scan over masters: active index and replica offsets
-    for (int m0 = 0; m0 < M; m0 += blockDim.x) {
-        const int m = m0 + tid;
+    // blocked scan over (hosted rank, master): active index and replica offsets
+    const int total_masters = nlocal * M;
+    for (int g0 = 0; g0 < total_masters; g0 += blockDim.x) {
+        const int gm = g0 + tid;
+        const int lr = gm < total_masters ? gm / M : 0;
+        const int m = gm < total_masters ? gm % M : 0;
+        const RankDev& rk = *call.rank[lr];
+        const PlanPtrs& plan = call.plan[lr];
+        const int me = rk.my_rank;
         int reps = 0;
-        if (m < M) {
+        if (gm < total_masters) {
             reps = plan.lcnts[me * M + m] - 1;
             reps = reps < 0 ? 0 : (reps > D - 1 ? D - 1 : reps);
         }
@@ -143,26 +152,26 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         if (act) {
             const int ai = a_off + a_incl - 1;
             const int rs = r_off + r_incl - reps;
-            sm.active_master[ai] = static_cast<short>(m);
             sm.rep_start[ai] = static_cast<short>(rs);
             const int l = me * M + m;
             for (int j = 0; j < reps && rs + j < kMaxSends; ++j) {
                 const int phys = plan.l2p[static_cast<int64_t>(l) * D + 1 + j];
-                int drank = phys / Lp, dslot = phys % Lp - M;
+                const int drank = phys / Lp, dslot = phys % Lp - M;
                 if (phys < 0 || drank >= N || dslot < 0 || dslot >= R) {  // never store outside a slot table
                     report_error(rk.status, UEP_DEV_BAD_PLAN, l);
-                    drank = -1;
-                    dslot = 0;
+                    sm.dst_weight[rs + j] = nullptr;
+                    sm.dst_scale[rs + j] = nullptr;
                 } else {
-                    atomicOr(&sm.send_mask[drank >> 5], 1u << (drank & 31));
+                    atomicOr(&sm.send_mask[lr][drank >> 5], 1u << (drank & 31));
+                    sm.dst_weight[rs + j] = rk.peer_replica_weight[drank] + static_cast<int64_t>(dslot) * sh.weight_slot_stride;
+                    sm.dst_scale[rs + j] = rk.peer_replica_scale[drank] + static_cast<int64_t>(dslot) * sh.scale_slot_stride;
                 }
-                sm.rep_rank[rs + j] = static_cast<short>(drank);
-                sm.rep_slot[rs + j] = static_cast<short>(dslot);
             }
-            // source alignment
-            for (int s = 0; s < sh.num_shards; ++s) {
-                if (sh.bytes[s] == 0) continue;
-                const uintptr_t p = static_cast<uintptr_t>(call.src_ptrs[local][s][m]);
+            // source addresses and their alignment
+            for (int s = 0; s < 4; ++s) {
+                const bool present = s < sh.num_shards && sh.bytes[s] != 0;
+                const uintptr_t p = present ? static_cast<uintptr_t>(call.src_ptrs[lr][s][m]) : 0;
+                sm.src[ai][s] = reinterpret_cast<const uint8_t*>(p);
                 if (p & 15u) atomicAnd(&sm.all_aligned, 0);
             }
         }
@@ -174,11 +183,13 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         __syncthreads();
     }
     if (tid == 0) sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxSends ? sm.total_reps : kMaxSends);
-    for (int s = tid; s < R; s += blockDim.x) {
-        const int l = plan.p2l[me * Lp + M + s];
+    for (int i = tid; i < nlocal * R; i += blockDim.x) {
+        const int lr = i / R, slot = i % R;
+        const int me = call.rank[lr]->my_rank;
+        const int l = call.plan[lr].p2l[me * Lp + M + slot];
         if (l >= 0) {
             const int src = l / M;
-            if (src >= 0 && src < N && src != me) atomicOr(&sm.recv_mask[src >> 5], 1u << (src & 31));
+            if (src >= 0 && src < N && src != me) atomicOr(&sm.recv_mask[lr][src >> 5], 1u << (src & 31));
         }
     }
     __syncthreads();
@@ -187,15 +198,15 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     int tiles_per_expert = 0;
     for (int s = 0; s < sh.num_shards; ++s) tiles_per_expert += shard_tiles[s];
     const int64_t total_tiles = static_cast<int64_t>(sm.n_active) * tiles_per_expert;
-    const int64_t first = cta, step = call.ctas_per_rank;
+    const int64_t first = blockIdx.x, step = gridDim.x;
     const int64_t count = first < total_tiles ? (total_tiles - first + step - 1) / step : 0;
+    DeviceStatus* status0 = call.rank[0]->status;
 
     if (sm.all_aligned) {
         if (tid == 0) {
             auto issue_load = [&](int64_t k) {
                 const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
-                const int m = sm.active_master[t.active];
-                const uint8_t* src = reinterpret_cast<const uint8_t*>(call.src_ptrs[local][t.shard][m]) + t.offset;
+                const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
                 const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
                 const int s = static_cast<int>(k % kSyncStages);
                 if (bytes16) {
@@ -208,17 +219,16 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             int64_t k = 0;
             for (; k < count; ++k) {
                 const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
-                const int m = sm.active_master[t.active];
                 const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
                 const int s = static_cast<int>(k % kSyncStages);
                 if (bytes16 && !mbar_wait(&bars[s], static_cast<uint32_t>((k / kSyncStages) & 1), call.timeout_ns)) break;
                 const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
                 for (int r = r0; r < r1; ++r) {
-                    if (sm.rep_rank[r] < 0) continue;
-                    uint8_t* dst = dest_addr(rk, sh, t.shard, sm.rep_rank[r], sm.rep_slot[r]) + t.offset;
+                    if (sm.dst_weight[r] == nullptr) continue;
+                    uint8_t* dst = dest_addr(sm, sh, t.shard, r) + t.offset;
                     if (bytes16) bulk_store(dst, smem_raw + s * kSyncTile, bytes16);
                     if (static_cast<uint32_t>(t.bytes) != bytes16) {  // up to 15 trailing bytes of a shard
-                        const uint8_t* src = reinterpret_cast<const uint8_t*>(call.src_ptrs[local][t.shard][m]) + t.offset;
+                        const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
                         for (int b = bytes16; b < t.bytes; ++b) dst[b] = src[b];
                     }
                 }
@@ -231,7 +241,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             }
             bulk_wait_all<0>();
             if (k < count) {
-                report_error(rk.status, UEP_DEV_TIMEOUT_COPY, static_cast<int>(k));
+                report_error(status0, UEP_DEV_TIMEOUT_COPY, static_cast<int>(k));
                 for (int64_t j = k; j < issued; ++j) {
                     mbar_wait(&bars[j % kSyncStages], static_cast<uint32_t>((j / kSyncStages) & 1), call.timeout_ns);
                 }
@@ -240,41 +250,48 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     } else {
         for (int64_t k = 0; k < count; ++k) {
             const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
-            const int m = sm.active_master[t.active];
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(call.src_ptrs[local][t.shard][m]) + t.offset;
+            const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
             const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
             for (int r = r0; r < r1; ++r) {
-                if (sm.rep_rank[r] < 0) continue;
-                copy_plain(src, dest_addr(rk, sh, t.shard, sm.rep_rank[r], sm.rep_slot[r]) + t.offset, t.bytes);
+                if (sm.dst_weight[r] == nullptr) continue;
+                copy_plain(src, dest_addr(sm, sh, t.shard, r) + t.offset, t.bytes);
             }
         }
     }
     __threadfence_system();
     __syncthreads();
 
-    // ---- completion: last CTA of the rank signals its receivers and waits for its senders
+    // ---- completion: the last CTA of the launch signals the receivers of every hosted rank
+    // and waits for their senders
+    int* ticket_ptr = call.rank[0]->sync_ticket;
     if (tid == 0) {
-        const int ticket = atomicAdd(rk.sync_ticket, 1);
-        if (ticket == call.ctas_per_rank - 1) {
-            *rk.sync_ticket = 0;
+        const int ticket = atomicAdd(ticket_ptr, 1);
+        if (ticket == static_cast<int>(gridDim.x) - 1) {
+            *ticket_ptr = 0;
             sm.is_last = 1;
         }
         __threadfence_system();
     }
     __syncthreads();
     if (!sm.is_last) return;
-    for (int p = tid; p < N; p += blockDim.x) {
-        if ((sm.send_mask[p >> 5] & (1u << (p & 31))) && me != call.withhold_rank) {
-            st_release_sys_u64(rk.peer_sync_flags[p] + me, call.epoch);
-        }
-    }
-    for (int p = tid; p < N; p += blockDim.x) {
-        if (sm.recv_mask[p >> 5] & (1u << (p & 31))) {
-            if (!wait_flag_ge(rk.peer_sync_flags[me] + p, call.epoch, call.timeout_ns)) atomicMax(&sm.timeout_peer, p);
+    for (int i = tid; i < nlocal * N; i += blockDim.x) {
+        const int lr = i / N, p = i % N;
+        const RankDev& rk = *call.rank[lr];
+        if ((sm.send_mask[lr][p >> 5] & (1u << (p & 31))) && rk.my_rank != call.withhold_rank) {
+            st_release_sys_u64(rk.peer_sync_flags[p] + rk.my_rank, call.epoch);
         }
     }
     __syncthreads();
-    if (tid == 0 && sm.timeout_peer >= 0) report_error(rk.status, UEP_DEV_TIMEOUT_SYNC, sm.timeout_peer);
+    for (int i = tid; i < nlocal * N; i += blockDim.x) {
+        const int lr = i / N, p = i % N;
+        const RankDev& rk = *call.rank[lr];
+        if (sm.recv_mask[lr][p >> 5] & (1u << (p & 31))) {
+            if (!wait_flag_ge(rk.peer_sync_flags[rk.my_rank] + p, call.epoch, call.timeout_ns)) {
+                atomicMax(&sm.timeout_peer, p);
+                report_error(rk.status, UEP_DEV_TIMEOUT_SYNC, p);
+            }
+        }
+    }
 }
 
 }  // namespace
@@ -294,15 +311,10 @@ cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
+    // Hosted ranks pool their tiles over all CTAs. The only waits are those of the last CTA,
+    // on flags that peers on other devices (or, for hosted ranks, this very CTA) write.
     const dim3 grid(call.nlocal * call.ctas_per_rank), block(kSyncThreads);
     count_launch();
-    if (call.nlocal > 1) {
-        // hosted ranks wait for each other's completion words: they must be co-resident
-        SyncCall copy = call;
-        void* args[] = {&copy};
-        return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(weight_sync_kernel), grid, block, args, smem,
-                                           stream);
-    }
     weight_sync_kernel<<<grid, block, smem, stream>>>(call);
     return cudaGetLastError();
 }

@@ -102,8 +102,7 @@ class SimGroup:
 
     def __init__(self, cfg: capi.Config):
         if not torch.cuda.is_available():
-            raise capi.UepError("SimGroup needs a CUDA device; there is no CPU implementation of this library")
-        assert cfg.sim_ranks == cfg.num_ranks
+            raise capi.UepError("a CUDA device is required; there is no CPU implementation of this library")
         self.lib = capi.lib()
         self.cfg = cfg
         self.N = cfg.num_ranks
@@ -115,8 +114,13 @@ class SimGroup:
         h = C.c_void_p()
         capi.check(self.lib.uep_manager_create(C.byref(cfg), C.byref(h)), "uep_manager_create")
         self.handle = h
-        capi.check(self.lib.uep_manager_connect(self.handle, None), "uep_manager_connect")
+        self._connect()
+        self.nlocal = self.lib.uep_manager_num_local(self.handle)
         self._keep = []  # pointer tables of the latest calls (must outlive the launches)
+
+    def _connect(self):
+        assert self.cfg.sim_ranks == self.cfg.num_ranks
+        capi.check(self.lib.uep_manager_connect(self.handle, None), "uep_manager_connect")
 
     # -- buffers ---------------------------------------------------------------------
     def buffer(self, rank: int, buffer_id: int) -> torch.Tensor:
@@ -201,7 +205,7 @@ class SimGroup:
         return code.value, detail.value
 
     def check_status(self):
-        for r in range(self.N):
+        for r in range(self.nlocal):
             code, detail = self.status(r)
             if code != 0:
                 raise capi.UepError(f"rank {r}: device status {code} ({capi.DEV_STATUS_NAMES.get(code, '?')}), "
@@ -220,3 +224,36 @@ class SimGroup:
             self.destroy()
         except Exception:
             pass
+
+
+class IpcGroup(SimGroup):
+    """One rank of a multi-process group (one process per GPU). The 64-byte cudaIpc handles of
+    the peer-visible arenas are all-gathered through the given torch.distributed group, which is
+    the only thing that group is used for. Per-call lists have one element: this rank's tensor."""
+
+    def __init__(self, cfg: capi.Config, group=None):
+        import torch.distributed as dist
+
+        self._dist = dist
+        self._pg = group
+        assert cfg.sim_ranks == 0
+        super().__init__(cfg)
+
+    def _connect(self):
+        dist = self._dist
+        handle = torch.zeros(capi.IPC_HANDLE_BYTES, dtype=torch.uint8)
+        capi.check(self.lib.uep_manager_export_handle(self.handle, handle.data_ptr()), "uep_manager_export_handle")
+        world = dist.get_world_size(self._pg)
+        backend = dist.get_backend(self._pg)
+        send = handle.to(self.device) if backend == "nccl" else handle
+        gathered = [torch.empty_like(send) for _ in range(world)]
+        dist.all_gather(gathered, send, group=self._pg)
+        blob = torch.stack([g.cpu() for g in gathered]).contiguous()
+        capi.check(self.lib.uep_manager_connect(self.handle, blob.data_ptr()), "uep_manager_connect")
+        dist.barrier(group=self._pg)  # every rank has mapped every arena before the first kernel
+
+    def destroy(self):
+        if self.handle:
+            torch.cuda.synchronize()
+            self._dist.barrier(group=self._pg)  # nobody unmaps while a peer may still write
+            super().destroy()

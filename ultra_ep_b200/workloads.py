@@ -74,6 +74,9 @@ CONFIGS = {
                                        redraw_popularity=True),
     # backward of the same layer (token-gradient gather + fp32 Wgrad reduce)
     "cfg4_qwen3_235b_bwd": LayerConfig("cfg4_qwen3_235b_bwd", 128, 8, 4, 8, 8192, 1.3, 4096, 1536, "fp8"),
+    # small stand-in of cfg3 for profiler captures (same kernel paths, a few hundred MB on the device)
+    "profile_small_fp8": LayerConfig("profile_small_fp8", 128, 8, 4, 8, 8192, 1.3, 2048, 768, "fp8",
+                                     redraw_popularity=True),
     # DeepSeek-V3-shaped extreme skew
     "cfg5_dsv3_stress": LayerConfig("cfg5_dsv3_stress", 256, 8, 8, 8, 16384, 1.5, 7168, 2048, "fp8",
                                     hot_expert_every_token=True, max_microbatches=4),
