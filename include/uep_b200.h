@@ -267,6 +267,13 @@ int uep_clear_status(uep_manager* m);
  * unbounded, csrc/kernels/weight_sync.cu:666-677, csrc/kernels/ptx.cuh:73-86). */
 int uep_debug_withhold_rank(uep_manager* m, int rank);
 
+/* Tuning aid: with UEP_SYNC_TRACE=1 in the environment when the manager is created, the
+ * weight_sync kernel records eight %globaltimer stamps per CTA (start, set-up done, copies
+ * issued, copies complete, fenced, ticket taken, flags done, unused); this copies the stamps of
+ * the first max_ctas CTAs of the latest launch to host memory [max_ctas][8]. No counterpart in
+ * the reference. */
+int uep_debug_sync_trace(uep_manager* m, unsigned long long* host_out, int max_ctas);
+
 /* Counters for benchmarks: kernels launched by this library since the last reset. */
 int64_t uep_launch_count(void);
 void uep_reset_launch_count(void);

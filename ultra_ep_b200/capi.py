@@ -104,6 +104,7 @@ SIGNATURES = {
     "uep_poll_status": (_i, [_vp, _i, C.POINTER(_i), C.POINTER(_i)]),
     "uep_clear_status": (_i, [_vp]),
     "uep_debug_withhold_rank": (_i, [_vp, _i]),
+    "uep_debug_sync_trace": (_i, [_vp, _vp, _i]),
     "uep_launch_count": (_i64, []),
     "uep_reset_launch_count": (None, []),
 }

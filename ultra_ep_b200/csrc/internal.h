@@ -63,6 +63,7 @@ struct PlanCall {
     uint64_t timeout_ns;
     int ctas_per_rank;
     int withhold_rank;  // test hook: this rank does not publish its flags (-1: none)
+    unsigned long long* trace;  // optional: 8 globaltimer stamps per hosted rank (tuning aid), or null
 };
 cudaError_t launch_plan(const PlanCall& call, cudaStream_t stream);
 int plan_ctas_per_rank(int input_kind, int max_T, int K_or_L, int nlocal, int num_sms);
@@ -78,6 +79,7 @@ struct SyncCall {
     uint64_t timeout_ns;
     int ctas_per_rank;
     int withhold_rank;  // test hook, as in PlanCall
+    unsigned long long* trace;  // optional: 8 globaltimer stamps per CTA (tuning aid), or null
 };
 cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream);
 int weight_sync_max_ctas_per_rank(int nlocal, int num_sms);

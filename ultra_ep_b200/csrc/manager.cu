@@ -39,7 +39,7 @@ struct RankHost {
     int32_t* plan_blob = nullptr;               // [layers][stride]
     int32_t* rank_quota_prefix = nullptr;       // [layers][L][D]
     int32_t* local_hist = nullptr;              // [Lpad]
-    int* tickets = nullptr;                     // [2]: plan, sync
+    int* tickets = nullptr;                     // [4]: plan ticket, sync ticket, sync tile counter, spare
     int32_t* global_loads = nullptr;            // [L]
     int32_t* loads_per_rank = nullptr;          // [N][L]
     DeviceStatus* status_host = nullptr;        // mapped pinned
@@ -73,6 +73,7 @@ struct uep_manager {
     int grad_reduce_ctas = 42;
     int weight_sync_ctas = 0;
     int withhold_rank = -1;
+    unsigned long long* sync_trace = nullptr;  // UEP_SYNC_TRACE=1: per-CTA phase stamps of the last weight_sync
 };
 
 namespace {
@@ -311,8 +312,8 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
         UEP_TRY_BAIL(cudaMalloc(&r.rank_quota_prefix, sizeof(int32_t) * static_cast<size_t>(m->L) * m->D * cfg->num_layers));
         UEP_TRY_BAIL(cudaMalloc(&r.local_hist, sizeof(int32_t) * m->Lpad));
         UEP_TRY_BAIL(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
-        UEP_TRY_BAIL(cudaMalloc(&r.tickets, sizeof(int) * 2));
-        UEP_TRY_BAIL(cudaMemset(r.tickets, 0, sizeof(int) * 2));
+        UEP_TRY_BAIL(cudaMalloc(&r.tickets, sizeof(int) * 4));
+        UEP_TRY_BAIL(cudaMemset(r.tickets, 0, sizeof(int) * 4));
         UEP_TRY_BAIL(cudaMalloc(&r.global_loads, sizeof(int32_t) * m->L));
         UEP_TRY_BAIL(cudaMemset(r.global_loads, 0, sizeof(int32_t) * m->L));
         UEP_TRY_BAIL(cudaMalloc(&r.loads_per_rank, sizeof(int32_t) * static_cast<size_t>(N) * m->L));
@@ -328,6 +329,12 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
             const int rc = uep_init_master_placement(p.p2l, p.l2p, p.lcnts, p.quota, p.quota_prefix,
                                                      p.rank_quota_prefix, N, M, R, m->D, nullptr);
             if (rc != UEP_OK) return bail(rc);
+        }
+    }
+    if (const char* tr = std::getenv("UEP_SYNC_TRACE")) {
+        if (tr[0] == '1') {
+            UEP_TRY_BAIL(cudaMalloc(&m->sync_trace, sizeof(unsigned long long) * 8 * 1024));
+            UEP_TRY_BAIL(cudaMemset(m->sync_trace, 0, sizeof(unsigned long long) * 8 * 1024));
         }
     }
     UEP_TRY_BAIL(cudaDeviceSynchronize());
@@ -386,6 +393,7 @@ int uep_manager_destroy(uep_manager* m) {
     if (m->comm_stream) cudaStreamDestroy(m->comm_stream);
     if (m->order_event) cudaEventDestroy(m->order_event);
     for (auto e : m->plan_ready) cudaEventDestroy(e);
+    cudaFree(m->sync_trace);
     delete m;
     return UEP_OK;
 }
@@ -468,6 +476,7 @@ int uep_update_placement(uep_manager* m, int layer_id, int input_kind, const voi
     call.timeout_ns = m->timeout_ns;
     call.ctas_per_rank = plan_ctas_per_rank(input_kind, max_T, K_or_L, m->nlocal, m->num_sms);
     call.withhold_rank = m->withhold_rank;
+    call.trace = m->sync_trace ? m->sync_trace + 8 * 1000 : nullptr;  // the last rows of the trace buffer
     UEP_CUDA_TRY(launch_plan(call, stream));
     const int slot = plan_slot(m, layer_id);
     UEP_CUDA_TRY(cudaEventRecord(m->plan_ready[slot], stream));
@@ -488,8 +497,11 @@ int uep_weight_sync(uep_manager* m, int layer_id, const int64_t* const* fc1_ptrs
     cudaStream_t current = static_cast<cudaStream_t>(current_stream);
     rc = begin_comm_op(m, wait_event, current);
     if (rc != UEP_OK) return rc;
-    rc = wait_for_plan(m, layer_id, m->comm_stream);
-    if (rc != UEP_OK) return rc;
+    // the plan was produced on `current` in the common case: the wait above already covers it
+    if (!(wait_event == nullptr && m->plan_stream[plan_slot(m, layer_id)] == current)) {
+        rc = wait_for_plan(m, layer_id, m->comm_stream);
+        if (rc != UEP_OK) return rc;
+    }
 
     SyncCall call;
     std::memset(&call, 0, sizeof(call));
@@ -516,6 +528,7 @@ int uep_weight_sync(uep_manager* m, int layer_id, const int64_t* const* fc1_ptrs
     call.timeout_ns = m->timeout_ns;
     call.ctas_per_rank = m->weight_sync_ctas;
     call.withhold_rank = m->withhold_rank;
+    call.trace = m->sync_trace;
     if (m->R > 0) UEP_CUDA_TRY(launch_weight_sync(call, m->comm_stream));
     return finish_sync_op(m, async_finish, current, done_event);
 }
@@ -530,8 +543,10 @@ int uep_grad_reduce(uep_manager* m, int layer_id, const int64_t* const* fc1_grad
     cudaStream_t current = static_cast<cudaStream_t>(current_stream);
     rc = begin_comm_op(m, wait_event, current);
     if (rc != UEP_OK) return rc;
-    rc = wait_for_plan(m, layer_id, m->comm_stream);
-    if (rc != UEP_OK) return rc;
+    if (!(wait_event == nullptr && m->plan_stream[plan_slot(m, layer_id)] == current)) {
+        rc = wait_for_plan(m, layer_id, m->comm_stream);
+        if (rc != UEP_OK) return rc;
+    }
     ReduceCall call;
     std::memset(&call, 0, sizeof(call));
     for (int i = 0; i < m->nlocal; ++i) {
@@ -677,6 +692,14 @@ int uep_poll_status(uep_manager* m, int local_rank, int* code, int* detail) {
     return UEP_OK;
 }
 
+int uep_debug_sync_trace(uep_manager* m, unsigned long long* host_out, int max_ctas) {
+    if (m == nullptr || host_out == nullptr || max_ctas <= 0) return fail(UEP_ERR_INVALID, "debug_sync_trace: bad argument");
+    if (m->sync_trace == nullptr) return fail(UEP_ERR_STATE, "debug_sync_trace: tracing is off (set UEP_SYNC_TRACE=1 before creating the manager)");
+    const int n = max_ctas < 1024 ? max_ctas : 1024;
+    UEP_CUDA_TRY(cudaMemcpy(host_out, m->sync_trace, sizeof(unsigned long long) * 8 * n, cudaMemcpyDeviceToHost));
+    return UEP_OK;
+}
+
 int uep_debug_withhold_rank(uep_manager* m, int rank) {
     if (m == nullptr) return fail(UEP_ERR_INVALID, "debug_withhold_rank: null manager");
     m->withhold_rank = rank;
@@ -691,7 +714,7 @@ int uep_clear_status(uep_manager* m) {
         r.status_host->detail = 0;
         // a timed-out plan may have left the exchange scratch half used: reset it
         UEP_CUDA_TRY(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
-        UEP_CUDA_TRY(cudaMemset(r.tickets, 0, sizeof(int) * 2));
+        UEP_CUDA_TRY(cudaMemset(r.tickets, 0, sizeof(int) * 4));
     }
     return UEP_OK;
 }

@@ -179,6 +179,10 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     __syncthreads();
     if (!s_is_last) return;
     __threadfence();
+    auto stamp = [&](int slot) {
+        if (call.trace != nullptr && tid == 0) call.trace[local * 8 + slot] = global_timer_ns();
+    };
+    stamp(0);
 
     // 2. the last CTA publishes the row to every rank (itself included) and resets the scratch
     const int slot = static_cast<int>(call.epoch & 1ull);
@@ -197,6 +201,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     __syncthreads();
     if (tid < N && me != call.withhold_rank) st_release_sys_u64(rk.peer_gather_flags[tid] + slot * N + me, call.epoch);
 
+    stamp(1);
     // 3. wait for every rank's row (bounded)
     if (tid < N) {
         const uint64_t* flag = rk.peer_gather_flags[me] + slot * N + tid;
@@ -208,6 +213,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
         return;  // plan of this layer is left as it was; the host raises on the status word
     }
 
+    stamp(2);
     // 4. reduce, expose the matrix, solve
     const int32_t* gathered = rk.peer_gather[me] + static_cast<int64_t>(slot) * N * Lpad;
     for (int i = tid; i < L; i += blockDim.x) {
@@ -222,6 +228,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     __threadfence_block();
     __syncthreads();
 
+    stamp(3);
     SolveArgs a;
     a.global_loads = rk.global_loads;
     a.loads_per_rank = rk.loads_per_rank;
@@ -237,6 +244,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     a.my_rank = me;
     const int num_domains = N / call.G;
     for (int d = 0; d < num_domains; ++d) solve_domain_dispatch(a, d, smem_raw, rk.status);
+    stamp(4);
 }
 
 size_t plan_smem_bytes(int N, int G, int M) {

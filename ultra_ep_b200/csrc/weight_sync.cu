@@ -19,6 +19,9 @@
 //     No CTA waits for another CTA of the same launch.
 // Pointers or sizes that are not multiples of 16 bytes take a plain vector/byte copy path.
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace uep {
@@ -26,8 +29,8 @@ namespace uep {
 namespace {
 
 constexpr int kSyncThreads = 128;
-constexpr int kSyncTile = 32 * 1024;
-constexpr int kSyncStages = 4;
+constexpr int kSyncTileDefault = 32 * 1024;
+constexpr int kSyncStagesDefault = 4;
 constexpr int kMaxSends = kMaxExportsPerDomain;  // replicas of one rank's masters never exceed G*R <= 512
 
 struct SyncShared {
@@ -53,6 +56,7 @@ struct TileRef {
     int bytes;       // bytes of this tile
 };
 
+template <int kSyncTile>
 __device__ __forceinline__ TileRef decode_tile(int64_t idx, int n_active, const ShardLayout& sh, const int* shard_tiles) {
     TileRef t;
     const int idx32 = static_cast<int>(idx);  // tile counts fit 32 bits (checked on the host side by construction)
@@ -86,6 +90,7 @@ __device__ void copy_plain(const uint8_t* src, uint8_t* dst, int bytes) {
     for (int i = done + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
 }
 
+template <int kSyncTile, int kSyncStages>
 __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call) {
     extern __shared__ __align__(128) char smem_raw[];  // kSyncStages * kSyncTile
     __shared__ SyncShared sm;
@@ -95,6 +100,10 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     const ShardLayout& sh = call.shards;
     const int M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N, nlocal = call.nlocal;
     const int tid = threadIdx.x;
+    auto stamp = [&](int slot) {
+        if (call.trace != nullptr && tid == 0) call.trace[blockIdx.x * 8 + slot] = global_timer_ns();
+    };
+    stamp(0);
 
     // ---- setup: send list of the hosted ranks from their plans ---------------------------
     if (tid == 0) {
@@ -194,34 +203,56 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     }
     __syncthreads();
 
+    stamp(1);
     // ---- copy -------------------------------------------------------------------------
     int tiles_per_expert = 0;
     for (int s = 0; s < sh.num_shards; ++s) tiles_per_expert += shard_tiles[s];
-    const int64_t total_tiles = static_cast<int64_t>(sm.n_active) * tiles_per_expert;
-    const int64_t first = blockIdx.x, step = gridDim.x;
-    const int64_t count = first < total_tiles ? (total_tiles - first + step - 1) / step : 0;
+    const int total_tiles = sm.n_active * tiles_per_expert;
     DeviceStatus* status0 = call.rank[0]->status;
+    // Tiles are handed out by an atomic counter: CTAs that run on busy SMs (the reroute and the
+    // model's own kernels run next to this one) simply take fewer, and replica counts that differ
+    // between masters cannot leave some CTAs with several times the work of others.
+    int* tile_counter = call.rank[0]->sync_ticket + 1;
 
     if (sm.all_aligned) {
         if (tid == 0) {
-            auto issue_load = [&](int64_t k) {
-                const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
+            int ring_tile[kSyncStages];  // tile index held by each stage (>= total_tiles: none)
+            // The index of the next tile is requested one load ahead, so the round trip of the
+            // atomic overlaps with the copies instead of sitting in front of every load.
+            int pending = atomicAdd(tile_counter, 1);
+            auto issue_load = [&](int s) {
+                const int idx = pending;
+                pending = idx < total_tiles ? atomicAdd(tile_counter, 1) : idx;
+                ring_tile[s] = idx;
+                if (idx >= total_tiles) return;
+                const TileRef t = decode_tile<kSyncTile>(idx, sm.n_active, sh, shard_tiles);
                 const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
                 const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
-                const int s = static_cast<int>(k % kSyncStages);
                 if (bytes16) {
                     mbar_expect_tx(&bars[s], bytes16);
                     bulk_load(smem_raw + s * kSyncTile, src, bytes16, &bars[s]);
                 }
             };
-            int64_t issued = count < kSyncStages - 1 ? count : kSyncStages - 1;
-            for (int64_t k = 0; k < issued; ++k) issue_load(k);
-            int64_t k = 0;
-            for (; k < count; ++k) {
-                const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
+#pragma unroll
+            for (int s = 0; s < kSyncStages; ++s) ring_tile[s] = total_tiles;
+#pragma unroll
+            for (int s = 0; s < kSyncStages - 1; ++s) issue_load(s);
+            uint32_t phase_bits = 0;  // bit s: parity the next wait on stage s expects
+            bool ok = true;
+            int k = 0;
+            while (true) {
+                const int s = k % kSyncStages;
+                const int idx = ring_tile[s];
+                if (idx >= total_tiles) break;  // indices are handed out in order: nothing is left
+                const TileRef t = decode_tile<kSyncTile>(idx, sm.n_active, sh, shard_tiles);
                 const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
-                const int s = static_cast<int>(k % kSyncStages);
-                if (bytes16 && !mbar_wait(&bars[s], static_cast<uint32_t>((k / kSyncStages) & 1), call.timeout_ns)) break;
+                if (bytes16) {
+                    if (!mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    phase_bits ^= 1u << s;
+                }
                 const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
                 for (int r = r0; r < r1; ++r) {
                     if (sm.dst_weight[r] == nullptr) continue;
@@ -233,23 +264,33 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                     }
                 }
                 bulk_commit();
-                if (issued < count) {
-                    if (k >= 1) bulk_wait_read<1>();
-                    issue_load(issued);
-                    ++issued;
-                }
+                // refill the stage that the previous tile's stores have finished reading
+                const int refill = (k + kSyncStages - 1) % kSyncStages;
+                if (k >= 1) bulk_wait_read<1>();
+                issue_load(refill);
+                ++k;
             }
+            stamp(2);
             bulk_wait_all<0>();
-            if (k < count) {
-                report_error(status0, UEP_DEV_TIMEOUT_COPY, static_cast<int>(k));
-                for (int64_t j = k; j < issued; ++j) {
-                    mbar_wait(&bars[j % kSyncStages], static_cast<uint32_t>((j / kSyncStages) & 1), call.timeout_ns);
+            stamp(3);
+            if (!ok) {
+                report_error(status0, UEP_DEV_TIMEOUT_COPY, k);
+                // loads still in flight must land before the shared memory is released
+                for (int j = 0; j < kSyncStages; ++j) {
+                    const int s = (k + j) % kSyncStages;
+                    if (ring_tile[s] < total_tiles) mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns);
                 }
             }
         }
     } else {
-        for (int64_t k = 0; k < count; ++k) {
-            const TileRef t = decode_tile(first + k * step, sm.n_active, sh, shard_tiles);
+        __shared__ int s_tile;
+        while (true) {
+            __syncthreads();
+            if (tid == 0) s_tile = atomicAdd(tile_counter, 1);
+            __syncthreads();
+            const int idx = s_tile;
+            if (idx >= total_tiles) break;
+            const TileRef t = decode_tile<kSyncTile>(idx, sm.n_active, sh, shard_tiles);
             const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
             const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
             for (int r = r0; r < r1; ++r) {
@@ -258,8 +299,11 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             }
         }
     }
-    __threadfence_system();
+    // Make this CTA's copies visible system-wide before it reports in. On the bulk-copy path
+    // only thread 0 issued copies and it has already waited for their completion.
+    if (!sm.all_aligned || tid == 0) __threadfence_system();
     __syncthreads();
+    stamp(4);
 
     // ---- completion: the last CTA of the launch signals the receivers of every hosted rank
     // and waits for their senders
@@ -267,12 +311,14 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     if (tid == 0) {
         const int ticket = atomicAdd(ticket_ptr, 1);
         if (ticket == static_cast<int>(gridDim.x) - 1) {
+            __threadfence();  // the other CTAs' copies, fenced before their tickets, are ordered before the flags
             *ticket_ptr = 0;
+            *tile_counter = 0;  // every CTA has stopped taking tiles
             sm.is_last = 1;
         }
-        __threadfence_system();
     }
     __syncthreads();
+    stamp(5);
     if (!sm.is_last) return;
     for (int i = tid; i < nlocal * N; i += blockDim.x) {
         const int lr = i / N, p = i % N;
@@ -292,31 +338,71 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             }
         }
     }
+    __syncthreads();
+    stamp(6);
+}
+
+// Tile / ring geometry. The default keeps 128 KiB of loads and stores in flight per CTA; the
+// environment variable UEP_SYNC_GEOMETRY=<tile KiB>x<stages> selects another compiled variant
+// (tuning aid).
+struct SyncGeometry {
+    int tile_kib, stages;
+    const void* fn;
+};
+const SyncGeometry kGeometries[] = {
+    {32, 4, reinterpret_cast<const void*>(weight_sync_kernel<32 * 1024, 4>)},
+    {16, 4, reinterpret_cast<const void*>(weight_sync_kernel<16 * 1024, 4>)},
+    {16, 8, reinterpret_cast<const void*>(weight_sync_kernel<16 * 1024, 8>)},
+    {8, 8, reinterpret_cast<const void*>(weight_sync_kernel<8 * 1024, 8>)},
+    {32, 6, reinterpret_cast<const void*>(weight_sync_kernel<32 * 1024, 6>)},
+    {64, 3, reinterpret_cast<const void*>(weight_sync_kernel<64 * 1024, 3>)},
+};
+
+const SyncGeometry& sync_geometry() {
+    static const SyncGeometry* chosen = nullptr;
+    if (chosen == nullptr) {
+        chosen = &kGeometries[0];
+        if (const char* env = std::getenv("UEP_SYNC_GEOMETRY")) {
+            int t = 0, st = 0;
+            if (std::sscanf(env, "%dx%d", &t, &st) == 2) {
+                for (const auto& g : kGeometries) {
+                    if (g.tile_kib == t && g.stages == st) chosen = &g;
+                }
+            }
+        }
+    }
+    return *chosen;
 }
 
 }  // namespace
 
 int weight_sync_max_ctas_per_rank(int nlocal, int num_sms) {
-    // one CTA per SM (128 KiB of shared memory each); hosted ranks share the device
-    const int per = num_sms / (nlocal > 0 ? nlocal : 1);
+    // CTAs that fit one wave: shared memory bounds the CTAs per SM; hosted ranks share the device
+    const SyncGeometry& g = sync_geometry();
+    const int smem = g.tile_kib * 1024 * g.stages + 30 * 1024;
+    int per_sm = (227 * 1024) / smem;
+    per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+    const int per = num_sms * per_sm / (nlocal > 0 ? nlocal : 1);
     return per < 1 ? 1 : per;
 }
 
 cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream) {
-    const size_t smem = static_cast<size_t>(kSyncStages) * kSyncTile;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(weight_sync_kernel),
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    const SyncGeometry& g = sync_geometry();
+    const size_t smem = static_cast<size_t>(g.stages) * g.tile_kib * 1024;
+    static const void* attr_set_for = nullptr;
+    if (attr_set_for != g.fn) {
+        cudaError_t e = cudaFuncSetAttribute(g.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        attr_set = true;
+        attr_set_for = g.fn;
     }
     // Hosted ranks pool their tiles over all CTAs. The only waits are those of the last CTA,
     // on flags that peers on other devices (or, for hosted ranks, this very CTA) write.
     const dim3 grid(call.nlocal * call.ctas_per_rank), block(kSyncThreads);
     count_launch();
-    weight_sync_kernel<<<grid, block, smem, stream>>>(call);
-    return cudaGetLastError();
+    SyncCall copy = call;
+    void* args[] = {&copy};
+    cudaError_t e = cudaLaunchKernel(g.fn, grid, block, args, smem, stream);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace uep
