@@ -119,6 +119,18 @@ int uep_sparse_reroute_i64(const int64_t* ids, int64_t* out, int T, int K, int L
                            const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
                            int32_t* scratch, void* stream);
 
+/* Same result as uep_sparse_reroute_i32 for callers that cannot allocate device memory where
+ * routing happens (a server whose memory pool owns the whole device, a frozen-allocator region,
+ * a plugin boundary that only forwards its tensors): the scratch lives in a fixed 1 MiB array
+ * inside the library image, so only inputs and outputs are passed and no allocation call of any
+ * kind is made. Refused with UEP_ERR_INVALID when ceil(T*K/2048)*L + 4 exceeds 262144 int32.
+ * All calls on a device share the array: calls that may overlap on the GPU must be ordered by
+ * the caller. The first call on a device looks up the array's device address; make it before
+ * any stream capture. This entry point has no counterpart in the reference. */
+int uep_sparse_reroute_i32_static(const int32_t* ids, int32_t* out, int T, int K, int L, const int32_t* l2p,
+                                  const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
+                                  void* stream);
+
 /* Row order of the (token,k) entries once grouped by physical expert (stable), and the
  * per-expert row offsets [P+1]. No counterpart in the reference (its dispatcher is external). */
 int uep_dispatch_positions(const int32_t* phys_ids, int64_t num_entries, int P, int32_t* pos,

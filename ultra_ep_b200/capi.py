@@ -78,6 +78,7 @@ SIGNATURES = {
     "uep_dense_reroute_backward": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "uep_sparse_reroute_i32": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "uep_sparse_reroute_i64": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "uep_sparse_reroute_i32_static": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "uep_dispatch_positions": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp]),
     "uep_dispatch_scratch_elems": (_i64, [_i64, _i]),
     "uep_gather_rows": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),

@@ -15,6 +15,9 @@
 // rule per (token, k) entry and therefore is deterministic, which the reference's
 // atomic-counter sparse kernel (reroute.cu:492-515) is not.
 
+#include <mutex>
+#include <string>
+
 #include "internal.h"
 
 namespace uep {
@@ -619,6 +622,62 @@ int uep_sparse_reroute_i64(const int64_t* ids, int64_t* out, int T, int K, int L
                            const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
                            int32_t* scratch, void* stream) {
     return sparse_common(2, ids, out, T, K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Sparse reroute for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc on the path where routing happens: an
+// inference server that has handed the whole device to its own memory pool, a caller inside
+// a region where the allocator is frozen, or a plugin boundary that only passes the tensors
+// it was given. The regular entry point needs a caller-provided scratch buffer (per-tile
+// expert counts); this variant keeps that scratch in a fixed array that is part of the
+// loaded library image on every device, so the caller passes inputs and outputs only.
+//
+// Limits and rules:
+//   * the per-tile counts must fit the array: ceil(T*K / 2048) * L + 4 <= 262144 int32 (1 MiB);
+//     e.g. 131072 entries (16384 tokens x top-8) with up to 4096 experts, or 1M entries with 512.
+//     Larger problems are refused with UEP_ERR_INVALID and a message, nothing is launched;
+//   * the array is shared by every call on a device and keeps the previous call's counts. The
+//     count pass overwrites every element the second pass reads, so nothing has to start at
+//     zero; but two calls that can overlap on the GPU (different streams without an ordering
+//     between them) would race on it: order them;
+//   * the first call on a device resolves the array's device address (once per device, with
+//     that device current). It launches nothing else extra, but it should be made before any
+//     stream capture begins.
+static constexpr int64_t kStaticRerouteScratchElems = 256 * 1024;
+static __device__ __align__(256) int32_t g_static_reroute_scratch[kStaticRerouteScratchElems];
+
+int uep_sparse_reroute_i32_static(const int32_t* ids, int32_t* out, int T, int K, int L, const int32_t* l2p,
+                                  const int32_t* lcnts, const int32_t* rank_quota_prefix, int D, int interleave,
+                                  void* stream) {
+    if (T < 0 || K < 0 || L <= 0 || D < 1) return fail(UEP_ERR_INVALID, "sparse_reroute_static: bad sizes");
+    const int64_t need = sparse_scratch_elems(static_cast<int64_t>(T) * K, L);
+    if (need > kStaticRerouteScratchElems) {
+        return fail(UEP_ERR_INVALID, "sparse_reroute_static: needs " + std::to_string(need) +
+                                         " int32 of scratch, the built-in array holds " +
+                                         std::to_string(kStaticRerouteScratchElems) +
+                                         " (use uep_sparse_reroute_i32 with your own scratch)");
+    }
+    // In host code the array's name is only a handle for the runtime: the address a kernel can
+    // use has to be asked for, per device, while that device is current.
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int32_t* device_ptr[kMaxDevices] = {nullptr};
+    int dev = -1;
+    UEP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(UEP_ERR_UNSUPPORTED, "sparse_reroute_static: device index above 63");
+    int32_t* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            UEP_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_reroute_scratch));
+            device_ptr[dev] = static_cast<int32_t*>(p);
+        }
+        scratch = device_ptr[dev];
+    }
+    return sparse_common(1, ids, out, T, K, L, l2p, lcnts, rank_quota_prefix, D, interleave, scratch, stream);
 }
 
 int64_t uep_dispatch_scratch_elems(int64_t num_entries, int P) { return sparse_tiles(num_entries) * (P + 1) + 4; }
