@@ -265,9 +265,7 @@ def run_ours(args):
     barrier()
     t_wall0 = time.perf_counter()
     for i in range(args.steps):
-        wl.flush_l2()
-        if world > 1:
-            dist.barrier()  # ranks enter the layer together, as they do after an all-to-all
+        wl.flush_l2()  # on the stream: no host synchronisation inside the timed region
         events.append(event_ms(torch, lambda: wl.step(i)))
     barrier()
     t_wall = time.perf_counter() - t_wall0
@@ -282,8 +280,6 @@ def run_ours(args):
     e2e_events = []
     for i in range(args.steps):
         wl.flush_l2()
-        if world > 1:
-            dist.barrier()
         e2e_events.append(event_ms(torch, lambda: wl.step_e2e(i)))
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -294,7 +290,7 @@ def run_ours(args):
     comm = group.comm_stream()
     plan_ms, sync_ms, reroute_ms = [], [], []
     rd = wr = 0
-    egress = ingress = 0
+    link_bytes = []  # per launch: the larger of this GPU's outbound and inbound bytes
     nb = min(args.steps, 16)
     for i in range(nb):
         layer = i % num_layers
@@ -304,14 +300,20 @@ def run_ours(args):
         a, b = event_ms(torch, lambda: group.update_placement(layer, ids))
         barrier()
         plan_ms.append(a.elapsed_time(b))
+        # weight_sync is timed right behind a plan issued on the same (communication) stream: the
+        # plan's load exchange has just lined the ranks up, and the two events bracket the kernel,
+        # not a cross-stream hand-over or the launch skew between processes
         wl.flush_l2()
         barrier()
-        a, b = event_ms(torch, lambda: group.weight_sync(layer, wl.tables[0], wl.tables[1], wl.tables[2], wl.tables[3]),
-                        stream=comm)
+        with torch.cuda.stream(comm):
+            group.update_placement(layer, ids)
+            a, b = event_ms(torch, lambda: group.weight_sync(layer, wl.tables[0], wl.tables[1], wl.tables[2], wl.tables[3]),
+                            stream=comm)
         barrier()
         sync_ms.append(a.elapsed_time(b))
         r_, w_, eg, ig = wl.sync_bytes(layer)
-        rd, wr, egress, ingress = rd + r_, wr + w_, egress + eg, ingress + ig
+        rd, wr = rd + r_, wr + w_
+        link_bytes.append(float(max(eg, ig)))
         wl.flush_l2()
         barrier()
         a, b = event_ms(torch, lambda: group.reroute_sparse(layer, ids, wl.phys_dev))
@@ -327,9 +329,17 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def max_over_ranks_each(xs):
+        if world == 1:
+            return list(xs)
+        t = torch.tensor(list(xs), dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
     mean_ms = max_over_ranks(mean_ms)
     e2e_ms = max_over_ranks(e2e_ms)
-    sync_total_ms = max_over_ranks(sum(sync_ms))
+    sync_each_ms = max_over_ranks_each(sync_ms)  # per launch: the slowest rank
+    sync_total_ms = sum(sync_each_ms)
     plan_mean = max_over_ranks(sum(plan_ms) / nb)
     reroute_mean = max_over_ranks(sum(reroute_ms) / nb)
     sync_mean = sync_total_ms / nb
@@ -342,13 +352,13 @@ def run_ours(args):
                     "algorithmic_bytes_per_launch": int(alg_bytes), "peak_source": peak_src + "; of measured",
                     "note": "simulated EP: peers are same-device buffers, bytes = reads + writes through HBM"}
     else:
-        busiest = max_over_ranks(float(max(egress, ingress)))
+        busiest = sum(max_over_ranks_each(link_bytes))  # per launch: the busiest GPU's link bytes
         achieved = busiest / 1e9 / (sync_total_ms / 1e3)
         roofline = {"kernel": "weight_sync_kernel", "bound": "nvlink", "achieved": round(achieved, 1),
                     "peak": NVLINK_PEER_GBS, "unit": "GB/s", "frac": round(achieved / NVLINK_PEER_GBS, 4),
                     "traffic": None, "algorithmic_bytes_per_launch": int(busiest / nb),
                     "peak_source": "measured peer copy on this pool, per direction (nominal 900); of measured",
-                    "note": "bytes = max(egress, ingress) of the busiest GPU; time = slowest rank"}
+                    "note": "per launch: bytes = max(egress, ingress) of the busiest GPU, time = slowest rank; summed over launches"}
 
     out = None
     if rank == 0:

@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
         const int m = gm < total_masters ? gm % M : 0;
         const RankDev& rk = *call.rank[lr];
         const PlanPtrs& plan = call.plan[lr];
-        const int me = rk.my_rank;
+        const int me = call.my_rank[lr];
         int reps = 0;
         if (gm < total_masters) {
             reps = plan.lcnts[me * M + m] - 1;

@@ -70,6 +70,7 @@ int plan_ctas_per_rank(int input_kind, int max_T, int K_or_L, int nlocal, int nu
 
 struct SyncCall {
     const RankDev* rank[kMaxLocalRanks];
+    int my_rank[kMaxLocalRanks];  // rank ids by value: one pointer hop less in every CTA's set-up
     PlanPtrs plan[kMaxLocalRanks];
     const int64_t* src_ptrs[kMaxLocalRanks][4];  // device int64[M] tables; scale tables may be null
     int nlocal;
@@ -86,6 +87,7 @@ int weight_sync_max_ctas_per_rank(int nlocal, int num_sms);
 
 struct ReduceCall {
     const RankDev* rank[kMaxLocalRanks];
+    int my_rank[kMaxLocalRanks];
     PlanPtrs plan[kMaxLocalRanks];
     const int64_t* fc1_grad_ptrs[kMaxLocalRanks];
     const int64_t* fc2_grad_ptrs[kMaxLocalRanks];

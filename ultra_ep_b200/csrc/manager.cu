@@ -508,6 +508,7 @@ int uep_weight_sync(uep_manager* m, int layer_id, const int64_t* const* fc1_ptrs
     for (int i = 0; i < m->nlocal; ++i) {
         if (fc1_ptrs[i] == nullptr || fc2_ptrs[i] == nullptr) return fail(UEP_ERR_INVALID, "weight_sync: null pointer table");
         call.rank[i] = m->ranks[i].dev;
+        call.my_rank[i] = m->ranks[i].rank;
         call.plan[i] = plan_ptrs(m, m->ranks[i], layer_id);
         call.src_ptrs[i][0] = fc1_ptrs[i];
         call.src_ptrs[i][1] = fc2_ptrs[i];
@@ -552,6 +553,7 @@ int uep_grad_reduce(uep_manager* m, int layer_id, const int64_t* const* fc1_grad
     for (int i = 0; i < m->nlocal; ++i) {
         if (fc1_grad_ptrs[i] == nullptr || fc2_grad_ptrs[i] == nullptr) return fail(UEP_ERR_INVALID, "grad_reduce: null pointer table");
         call.rank[i] = m->ranks[i].dev;
+        call.my_rank[i] = m->ranks[i].rank;
         call.plan[i] = plan_ptrs(m, m->ranks[i], layer_id);
         call.fc1_grad_ptrs[i] = fc1_grad_ptrs[i];
         call.fc2_grad_ptrs[i] = fc2_grad_ptrs[i];

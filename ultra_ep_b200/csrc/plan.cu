@@ -242,6 +242,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     a.locality = call.params.locality_aware;
     a.eps = call.params.oracle_eps;
     a.my_rank = me;
+    a.trace = call.trace != nullptr ? call.trace + (kMaxLocalRanks + local) * 8 : nullptr;
     const int num_domains = N / call.G;
     for (int d = 0; d < num_domains; ++d) solve_domain_dispatch(a, d, smem_raw, rk.status);
     stamp(4);
@@ -355,6 +356,7 @@ int uep_solve_placement(const int32_t* loads_per_rank, int32_t* global_loads_out
     a.locality = params->locality_aware;
     a.eps = params->oracle_eps;
     a.my_rank = my_rank;
+    a.trace = nullptr;
     const size_t smem = solver_smem_bytes(nvl_ranks * M, nvl_ranks) + 16;
     UEP_CUDA_TRY(ensure_smem(reinterpret_cast<const void*>(solve_kernel), smem));
     count_launch();

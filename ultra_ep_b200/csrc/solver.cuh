@@ -40,6 +40,7 @@ struct SolveArgs {
     int locality;
     float eps;
     int my_rank;
+    unsigned long long* trace;  // optional: 8 globaltimer stamps of the solver phases (tuning aid), or null
 };
 
 constexpr int kSolverProbeWarps = 4;
@@ -216,23 +217,25 @@ __device__ bool warp_build_plan(const SolverSmem& sm, int32_t* export_sum, uint3
 // Split of this rank's tokens of one expert over the expert's replicas, as an inclusive
 // prefix. Semantics of csrc/kernels/placement.cu:1342-1481 / :669-786 of the reference.
 template <int MAXC>
-__device__ void build_rank_quota_prefix(const SolveArgs& a, int l_global, int C, int my_load, int domain_start_rank,
-                                        int Lp, int L) {
+__device__ void build_rank_quota_prefix(const SolveArgs& a, int l_global, int C, int my_load, const int* phys,
+                                        const int* q, int Lp, int L) {
+    // phys[j] / q[j]: physical id and quota of replica j (j = 0 is the master), handed over from
+    // shared memory by the caller so that no plan row has to be read back from global memory.
     const int64_t row = static_cast<int64_t>(l_global) * a.D;
     int host_rank[MAXC], my_alloc[MAXC];
     long long remainders[MAXC];
     for (int j = 0; j < C; ++j) {
-        host_rank[j] = a.l2p[row + j] / Lp;
+        host_rank[j] = phys[j] / Lp;
         my_alloc[j] = 0;
         remainders[j] = -1;
     }
     if (!a.locality) {
         const int rem_my = my_load;
         int assigned = 0, total_quota = 0;
-        for (int j = 0; j < C; ++j) total_quota += a.quota[row + j];
+        for (int j = 0; j < C; ++j) total_quota += q[j];
         if (rem_my > 0 && total_quota > 0) {
             for (int j = 0; j < C; ++j) {
-                const long long scaled = static_cast<long long>(rem_my) * a.quota[row + j];
+                const long long scaled = static_cast<long long>(rem_my) * q[j];
                 const int share = static_cast<int>(scaled / total_quota);
                 my_alloc[j] = share;
                 remainders[j] = scaled % total_quota;
@@ -267,17 +270,16 @@ __device__ void build_rank_quota_prefix(const SolveArgs& a, int l_global, int C,
             if (f == j) {
                 host_left[j] = __ldcg(a.loads_per_rank + static_cast<int64_t>(host_rank[j]) * L + l_global);
             }
-            const int q = a.quota[row + j];
-            const int local_fill = min(host_left[f], q);
+            const int qj = q[j];
+            const int local_fill = min(host_left[f], qj);
             host_left[f] -= local_fill;
-            remote_cap[j] = q - local_fill;
+            remote_cap[j] = qj - local_fill;
             total_remote_cap += remote_cap[j];
             if (host_rank[j] == a.my_rank) {
                 my_alloc[j] += local_fill;
                 rem_my -= local_fill;
             }
         }
-        (void)domain_start_rank;
         rem_my = max(rem_my, 0);
         if (rem_my > 0 && total_remote_cap > 0) {
             int assigned = 0;
@@ -325,6 +327,10 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
     const int domain_start_rank = domain * G;
     const int domain_start_log = domain_start_rank * M;
     SolverSmem sm = carve_solver_smem(smem_raw, E, G);
+    auto stamp = [&](int slot) {
+        if (a.trace != nullptr && tid == 0) a.trace[slot] = global_timer_ns();
+    };
+    stamp(0);
 
     // Clear this domain's slice of every output, then place the masters.
     for (int i = tid; i < G * Lp; i += nthreads) a.p2l[domain_start_rank * Lp + i] = -1;
@@ -346,6 +352,7 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
         a.l2p[static_cast<int64_t>(l_global) * D] = phys;
     }
     __syncthreads();
+    stamp(1);
     for (int r = tid; r < G; r += nthreads) {
         int sum = 0;
         for (int m = 0; m < M; ++m) sum += sm.loads[r * M + m];
@@ -394,6 +401,7 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
     }
     __syncthreads();
 
+    stamp(2);
     const bool allow0 = a.allow_zero_master != 0;
     if (do_search) {
         if (warp == 0) {  // fast path: up to three builds with the dynamic floor
@@ -524,6 +532,7 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
         }
     }
 
+    stamp(3);
     // Emit: master quotas, then replicas in plan order.
     for (int e = tid; e < E; e += nthreads) {
         const int64_t row = static_cast<int64_t>(domain_start_log + e) * D;
@@ -546,23 +555,61 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
             a.p2l[phys] = l_global;
             a.l2p[row + slot] = phys;
             a.quota[row + slot] = entry.quota;
+            sm.plan[k].target_rank_local = phys;  // from here on the entry carries the physical id
         }
     }
     __syncthreads();
+    stamp(4);
+    const int n_exports = sm.ctrl[kCtlNumExports];
     for (int e = tid; e < E; e += nthreads) {
         const int l_global = domain_start_log + e;
         const int64_t row = static_cast<int64_t>(l_global) * D;
         const int C = min(sm.expert_slot[e], D);
         a.lcnts[l_global] = C;
-        int prefix = 0;
-        for (int j = 0; j < C; ++j) {
-            prefix += a.quota[row + j];
-            a.quota_prefix[row + j] = prefix;
+        const int master_quota = do_search ? (sm.loads[e] - sm.export_sum[e]) : sm.loads[e];
+        const int master_phys = (domain_start_rank + e / M) * Lp + e % M;
+        if (C <= 8) {
+            int phys[8], q[8];
+            phys[0] = master_phys;
+            q[0] = master_quota;
+            int j = 1;
+            if (C > 1) {
+                for (int k = 0; k < n_exports && j < C; ++k) {
+                    if (sm.plan[k].expert_local == e) {
+                        phys[j] = sm.plan[k].target_rank_local;
+                        q[j] = sm.plan[k].quota;
+                        ++j;
+                    }
+                }
+            }
+            int prefix = 0;
+            for (int jj = 0; jj < C; ++jj) {
+                prefix += q[jj];
+                a.quota_prefix[row + jj] = prefix;
+            }
+            build_rank_quota_prefix<8>(a, l_global, C, sm.my_loads[e], phys, q, Lp, L);
+        } else {
+            int phys[kMaxRanksPerDomain], q[kMaxRanksPerDomain];
+            phys[0] = master_phys;
+            q[0] = master_quota;
+            int j = 1;
+            for (int k = 0; k < n_exports && j < C; ++k) {
+                if (sm.plan[k].expert_local == e) {
+                    phys[j] = sm.plan[k].target_rank_local;
+                    q[j] = sm.plan[k].quota;
+                    ++j;
+                }
+            }
+            int prefix = 0;
+            for (int jj = 0; jj < C; ++jj) {
+                prefix += q[jj];
+                a.quota_prefix[row + jj] = prefix;
+            }
+            build_rank_quota_prefix<kMaxRanksPerDomain>(a, l_global, C, sm.my_loads[e], phys, q, Lp, L);
         }
-        if (C <= 8) build_rank_quota_prefix<8>(a, l_global, C, sm.my_loads[e], domain_start_rank, Lp, L);
-        else build_rank_quota_prefix<kMaxRanksPerDomain>(a, l_global, C, sm.my_loads[e], domain_start_rank, Lp, L);
     }
     __syncthreads();
+    stamp(5);
 }
 
 __device__ inline void solve_domain_dispatch(const SolveArgs& a, int domain, char* smem_raw, DeviceStatus* status) {

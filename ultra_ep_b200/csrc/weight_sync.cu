@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         const int m = gm < total_masters ? gm % M : 0;
         const RankDev& rk = *call.rank[lr];
         const PlanPtrs& plan = call.plan[lr];
-        const int me = rk.my_rank;
+        const int me = call.my_rank[lr];
         int reps = 0;
         if (gm < total_masters) {
             reps = plan.lcnts[me * M + m] - 1;
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     if (tid == 0) sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxSends ? sm.total_reps : kMaxSends);
     for (int i = tid; i < nlocal * R; i += blockDim.x) {
         const int lr = i / R, slot = i % R;
-        const int me = call.rank[lr]->my_rank;
+        const int me = call.my_rank[lr];
         const int l = call.plan[lr].p2l[me * Lp + M + slot];
         if (l >= 0) {
             const int src = l / M;
@@ -299,9 +299,11 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             }
         }
     }
-    // Make this CTA's copies visible system-wide before it reports in. On the bulk-copy path
-    // only thread 0 issued copies and it has already waited for their completion.
-    if (!sm.all_aligned || tid == 0) __threadfence_system();
+    // Order this CTA's copies before its ticket. On the bulk-copy path only thread 0 issued
+    // copies and it has already waited for their completion.
+    // Device scope is enough here: the ticket below hands these writes to the last CTA, whose
+    // system-scope release of the flags then covers them (causality is transitive across scopes).
+    if (!sm.all_aligned || tid == 0) __threadfence();
     __syncthreads();
     stamp(4);
 
