@@ -292,20 +292,20 @@ def run_ours(args):
     rd = wr = 0
     link_bytes = []  # per launch: the larger of this GPU's outbound and inbound bytes
     nb = min(args.steps, 16)
+    # Each operation is queued right behind the L2 flush (no host synchronisation in between), so
+    # its events bracket the kernels, not the latency of a launch into an idle GPU.
     for i in range(nb):
         layer = i % num_layers
         ids = wl.ids_dev[i % len(wl.ids_dev)]
-        wl.flush_l2()
         barrier()
+        wl.flush_l2()
         a, b = event_ms(torch, lambda: group.update_placement(layer, ids))
         barrier()
         plan_ms.append(a.elapsed_time(b))
         # weight_sync is timed right behind a plan issued on the same (communication) stream: the
-        # plan's load exchange has just lined the ranks up, and the two events bracket the kernel,
-        # not a cross-stream hand-over or the launch skew between processes
-        wl.flush_l2()
-        barrier()
+        # plan's load exchange has just lined the ranks up, and there is no cross-stream hand-over
         with torch.cuda.stream(comm):
+            wl.flush_l2()
             group.update_placement(layer, ids)
             a, b = event_ms(torch, lambda: group.weight_sync(layer, wl.tables[0], wl.tables[1], wl.tables[2], wl.tables[3]),
                             stream=comm)
@@ -315,7 +315,6 @@ def run_ours(args):
         rd, wr = rd + r_, wr + w_
         link_bytes.append(float(max(eg, ig)))
         wl.flush_l2()
-        barrier()
         a, b = event_ms(torch, lambda: group.reroute_sparse(layer, ids, wl.phys_dev))
         barrier()
         reroute_ms.append(a.elapsed_time(b))
@@ -390,10 +389,162 @@ def run_ours(args):
         if ref is not None:
             out["ref_sm100"] = ref
     group.destroy()
+    del wl
+    torch.cuda.empty_cache()
+    if not args.no_backward:
+        backward = run_backward(args, world, rank, dev, peak_hbm, max_over_ranks_each)
+        if out is not None:
+            out["backward"] = backward
     if world > 1:
         dist.destroy_process_group()
     if out is not None:
         print(json.dumps(out))
+
+
+# ------------------------------------------------------------------------------------------
+# backward path (secondary figures)
+# ------------------------------------------------------------------------------------------
+def run_backward(args, world, rank, dev, peak_hbm, max_over_ranks_each):
+    """Backward balancing path of the same layer shape: dense reroute backward (probability
+    gradients [T,P] -> [T,L]), the token-gradient row gather ([T*K, hidden] bf16, physical-expert
+    order back to (token,k) order) and the fp32 Wgrad reduce of the replicas into their masters.
+    Returns per-operation times and the rooflines of the gather and of the reduce."""
+    import torch
+    import torch.distributed as dist
+
+    from ultra_ep_b200 import capi, sim
+    from ultra_ep_b200 import workloads as W
+
+    lib = capi.lib()
+    base = W.CONFIGS["cfg4_qwen3_235b_bwd"]
+    cfg = base.with_ep(world) if world > 1 else base
+    N, M, R, L = cfg.ep, cfg.masters, cfg.redundant, cfg.num_experts
+    P = N * (M + R)
+    mcfg = sim.make_config(N, M, R, 1, fc1_numel=cfg.fc1_numel, fc2_numel=cfg.fc2_numel,
+                           weight_elem_bytes=cfg.weight_elem_bytes, fc1_scale_numel=cfg.fc1_scale_numel,
+                           fc2_scale_numel=cfg.fc2_scale_numel, is_train=True, rank=rank, sim=(world == 1),
+                           grad_reduce_num_sms=args.reduce_sms)
+    group = sim.SimGroup(mcfg) if world == 1 else sim.IpcGroup(mcfg, dist.group.WORLD)
+    ranks = list(range(N)) if world == 1 else [rank]
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    flush_read = torch.zeros(FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
+
+    def flush_l2():
+        flush.zero_()
+        flush_read.sum()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    ids = [torch.from_numpy(W.routing_ids(cfg, r)).to(dev) for r in ranks]
+    group.update_placement(0, ids)
+    phys = group.reroute_sparse(0, ids)
+    barrier()
+    reps = 6
+    out = {"workload": f"{cfg.name}: backward of the same layer, " + ("EP8 simulated on one GPU" if world == 1 else f"EP{world}")}
+
+    # -- Wgrad reduce ------------------------------------------------------------------------
+    numel = cfg.fc1_numel + cfg.fc2_numel
+    g1 = [torch.full((M, cfg.fc1_numel), 1e-4, dtype=torch.float32, device=dev) for _ in ranks]
+    g2 = [torch.full((M, cfg.fc2_numel), 1e-4, dtype=torch.float32, device=dev) for _ in ranks]
+    t1 = group.pointer_tables([[g[m] for m in range(M)] for g in g1])
+    t2 = group.pointer_tables([[g[m] for m in range(M)] for g in g2])
+    for li in range(len(ranks)):
+        group.buffer(li, capi.BUF_REPLICA_GRAD).fill_(1e-4)
+    hbm_bytes = 0
+    link = 0
+    for li, r in enumerate(ranks):
+        lc = group.buffer(li, capi.BUF_LCNTS)[0].cpu().numpy()
+        p2l = group.buffer(li, capi.BUF_P2L)[0].cpu().numpy().reshape(N, M + R)
+        mine = lc[r * M:(r + 1) * M]
+        n_rep = int((mine - 1).clip(min=0).sum())
+        hbm_bytes += int((mine > 1).sum()) * 8 * numel + n_rep * 8 * numel  # masters read+written; replicas read+zeroed
+        used = int((p2l[r, M:] >= 0).sum())
+        link = max(link, n_rep * 4 * numel, used * 4 * numel)
+    comm = group.comm_stream()
+    red = []
+    for it in range(3 + reps):
+        barrier()
+        with torch.cuda.stream(comm):
+            flush_l2()
+            a, b = event_ms(torch, lambda: group.grad_reduce(0, t1, t2), stream=comm)
+        barrier()
+        if it >= 3:
+            red.append(a.elapsed_time(b))
+    group.check_status()
+    red = max_over_ranks_each(red)
+    red_ms = sum(red) / len(red)
+    out["grad_reduce_us"] = round(red_ms * 1e3, 1)
+    if world == 1:
+        ach = hbm_bytes / 1e9 / (red_ms / 1e3)
+        out["grad_reduce_roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": peak_hbm, "unit": "GB/s",
+                                       "frac": round(ach / peak_hbm, 4), "algorithmic_bytes_per_launch": hbm_bytes,
+                                       "ctas": args.reduce_sms,
+                                       "note": "simulated EP: masters read+written, replicas read+zeroed, all through HBM"}
+    else:
+        busiest = max(max_over_ranks_each([float(link)]))
+        ach = busiest / 1e9 / (red_ms / 1e3)
+        out["grad_reduce_roofline"] = {"bound": "nvlink", "achieved": round(ach, 1), "peak": NVLINK_PEER_GBS, "unit": "GB/s",
+                                       "frac": round(ach / NVLINK_PEER_GBS, 4), "algorithmic_bytes_per_launch": int(busiest),
+                                       "ctas": args.reduce_sms,
+                                       "note": "bytes = replica gradients the busiest GPU pulls in (it pushes as many zeros)"}
+    del g1, g2, t1, t2
+
+    # -- token-gradient gather (one rank's rows per launch) ------------------------------------
+    H = cfg.hidden
+    rows = cfg.tokens_per_rank * cfg.topk
+    src = torch.empty((rows, H), dtype=torch.bfloat16, device=dev).normal_(0, 1e-3)
+    dst = torch.empty_like(src)
+    pos = torch.empty(rows, dtype=torch.int32, device=dev)
+    offs = torch.empty(P + 1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(int(lib.uep_dispatch_scratch_elems(rows, P)), dtype=torch.int32, device=dev)
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    pos_t, gat_t = [], []
+    for it in range(3 + reps):
+        barrier()
+        flush_l2()
+        a, b = event_ms(torch, lambda: capi.check(lib.uep_dispatch_positions(
+            phys[0].data_ptr(), rows, P, pos.data_ptr(), offs.data_ptr(), scratch.data_ptr(), st), "uep_dispatch_positions"))
+        c, d = event_ms(torch, lambda: capi.check(lib.uep_gather_rows(
+            src.data_ptr(), pos.data_ptr(), dst.data_ptr(), rows, rows, H * 2, status.data_ptr(), st), "uep_gather_rows"))
+        barrier()
+        if it >= 3:
+            pos_t.append(a.elapsed_time(b))
+            gat_t.append(c.elapsed_time(d))
+    if int(status[0].item()) != 0:
+        raise RuntimeError("uep_gather_rows reported an out-of-range row index")
+    gat = max_over_ranks_each(gat_t)
+    gat_ms = sum(gat) / len(gat)
+    gbytes = 2 * rows * H * 2
+    ach = gbytes / 1e9 / (gat_ms / 1e3)
+    out["dispatch_positions_us"] = round(sum(pos_t) / len(pos_t) * 1e3, 1)
+    out["gather_rows_us"] = round(gat_ms * 1e3, 1)
+    out["gather_rows_roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": peak_hbm, "unit": "GB/s",
+                                   "frac": round(ach / peak_hbm, 4), "algorithmic_bytes_per_launch": gbytes,
+                                   "note": f"[{rows},{H}] bf16 rows read once and written once, one rank per launch"}
+    del src, dst
+
+    # -- dense reroute backward (probability gradients) ---------------------------------------
+    maps = [torch.from_numpy(W.ids_to_map(x.cpu().numpy(), L)).to(dev) for x in ids]
+    probs = [torch.rand(m.shape, dtype=torch.float32, device=dev) * m for m in maps]
+    ex_probs, ex_maps = group.reroute_dense(0, maps, probs)
+    grads = [torch.rand_like(p_) for p_ in ex_probs]
+    bwd = []
+    for it in range(3 + reps):
+        barrier()
+        flush_l2()
+        a, b = event_ms(torch, lambda: group.reroute_dense_backward(0, grads, maps, ex_maps))
+        barrier()
+        if it >= 3:
+            bwd.append(a.elapsed_time(b))
+    bwd = max_over_ranks_each(bwd)
+    out["dense_reroute_backward_us"] = round(sum(bwd) / len(bwd) * 1e3, 1)
+    group.check_status()
+    group.destroy()
+    return out
 
 
 # ------------------------------------------------------------------------------------------
@@ -584,6 +735,8 @@ def main():
     ap.add_argument("--cpu-budget-s", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--no-backward", action="store_true", help="skip the backward-path figures (cfg4)")
+    ap.add_argument("--reduce-sms", type=int, default=42, help="CTAs of the Wgrad reduce kernel (reference default 42)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -70,6 +70,37 @@ __device__ __forceinline__ bool wait_flag_ge(const uint64_t* flag, uint64_t targ
     }
 }
 
+// A 64-bit word that carries its own validity: high half = epoch tag, low half = payload.
+// An aligned 8-byte store is single-copy atomic, so a reader that sees the tag sees the
+// payload: no fence and no separate flag are needed between the two.
+__device__ __forceinline__ uint64_t ld_relaxed_sys_u64(const uint64_t* p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_u64(uint64_t* p, uint64_t v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t tag_word(uint32_t tag, uint32_t payload) {
+    return (static_cast<uint64_t>(tag) << 32) | payload;
+}
+// Spin until the word at p carries `tag` or the time limit passes. Returns true on success and
+// leaves the word in `w`.
+__device__ __forceinline__ bool wait_tagged_word(const uint64_t* p, uint32_t tag, uint64_t timeout_ns, uint64_t& w) {
+    w = ld_relaxed_sys_u64(p);
+    if (static_cast<uint32_t>(w >> 32) == tag) return true;
+    const uint64_t start = global_timer_ns();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            w = ld_relaxed_sys_u64(p);
+            if (static_cast<uint32_t>(w >> 32) == tag) return true;
+            __nanosleep(20);
+        }
+        if (global_timer_ns() - start > timeout_ns) return false;
+    }
+}
+
 // ---------------------------------------------------------------------------------
 // mbarrier + bulk async copies (non-multicast, 1-D). Addresses and sizes must be
 // multiples of 16 bytes; callers check and take a plain-load path otherwise.

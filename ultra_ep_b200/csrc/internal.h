@@ -22,8 +22,7 @@ struct RankDev {
     // plan exchange
     int32_t* local_hist;     // [Lpad], zero between calls
     int* plan_ticket;        // zero between calls
-    int32_t* peer_gather[kMaxPeers];  // each: [2][N][Lpad] int32
-    uint64_t* peer_gather_flags[kMaxPeers];  // each: [2][N]
+    uint64_t* peer_gather[kMaxPeers];  // each: [2][N][Lpad] words, (epoch tag << 32) | token count
     int32_t* global_loads;   // [L]
     int32_t* loads_per_rank; // [N][L] latest gathered matrix (contiguous copy)
     // weight sync / grad reduce

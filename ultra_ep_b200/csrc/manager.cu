@@ -28,7 +28,7 @@ struct uep_event {
 namespace {
 
 struct ArenaLayout {
-    size_t gather, gather_flags, sync_flags, replica_weight, replica_scale, replica_grad, total;
+    size_t gather, sync_flags, replica_weight, replica_scale, replica_grad, total;
 };
 
 struct RankHost {
@@ -143,8 +143,7 @@ int upload_rank_dev(uep_manager* m, RankHost& r) {
     for (int p = 0; p < m->N; ++p) {
         uint8_t* base = static_cast<uint8_t*>(r.peer_arena[p]);
         if (base == nullptr) return fail(UEP_ERR_STATE, "connect: a peer arena is not mapped");
-        d.peer_gather[p] = reinterpret_cast<int32_t*>(base + m->arena.gather);
-        d.peer_gather_flags[p] = reinterpret_cast<uint64_t*>(base + m->arena.gather_flags);
+        d.peer_gather[p] = reinterpret_cast<uint64_t*>(base + m->arena.gather);
         d.peer_sync_flags[p] = reinterpret_cast<uint64_t*>(base + m->arena.sync_flags);
         d.peer_replica_weight[p] = base + m->arena.replica_weight;
         d.peer_replica_scale[p] = base + m->arena.replica_scale;
@@ -282,8 +281,7 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
 
     // arena layout (identical on every rank, so offsets need not be exchanged)
     size_t off = 0;
-    m->arena.gather = off;        off = align256(off + sizeof(int32_t) * 2 * N * m->Lpad);
-    m->arena.gather_flags = off;  off = align256(off + sizeof(uint64_t) * 2 * N);
+    m->arena.gather = off;        off = align256(off + sizeof(uint64_t) * 2 * N * m->Lpad);
     m->arena.sync_flags = off;    off = align256(off + sizeof(uint64_t) * N);
     m->arena.replica_weight = off; off = align256(off + static_cast<size_t>(R) * m->weight_stride);
     m->arena.replica_scale = off;  off = align256(off + static_cast<size_t>(R) * m->scale_stride);

@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     const int L = N * M;
     const int Lpad = (L + 3) / 4 * 4;
     const int tid = threadIdx.x;
+    const unsigned long long t_start = call.trace != nullptr ? global_timer_ns() : 0ull;
 
     // 1. histogram slice -> shared -> this rank's row in global memory
     int32_t* hist = reinterpret_cast<int32_t*>(smem_raw);
@@ -183,9 +184,13 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
         if (call.trace != nullptr && tid == 0) call.trace[local * 8 + slot] = global_timer_ns();
     };
     stamp(0);
+    if (call.trace != nullptr && tid == 0) call.trace[local * 8 + 5] = t_start;  // when this CTA started
 
-    // 2. the last CTA publishes the row to every rank (itself included) and resets the scratch
+    // 2. the last CTA publishes the row to every rank (itself included) and resets the scratch.
+    //    Every 64-bit word carries the epoch beside its count, so a row needs neither a fence nor
+    //    a flag: one NVLink crossing, and the reader knows a word is this layer's when it sees it.
     const int slot = static_cast<int>(call.epoch & 1ull);
+    const uint32_t tag = static_cast<uint32_t>(call.epoch);
     const int me = rk.my_rank;
     for (int i = tid; i < L; i += blockDim.x) {
         hist[i] = __ldcg(rk.local_hist + i);
@@ -193,20 +198,44 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     }
     if (tid == 0) *rk.plan_ticket = 0;
     __syncthreads();
-    for (int idx = tid; idx < N * L; idx += blockDim.x) {
-        const int p = idx / L, i = idx % L;
-        rk.peer_gather[p][(static_cast<int64_t>(slot) * N + me) * Lpad + i] = hist[i];
+    if (me != call.withhold_rank) {
+        for (int idx = tid; idx < N * L; idx += blockDim.x) {
+            const int p = idx / L, i = idx % L;
+            st_relaxed_sys_u64(rk.peer_gather[p] + (static_cast<int64_t>(slot) * N + me) * Lpad + i,
+                               tag_word(tag, static_cast<uint32_t>(hist[i])));
+        }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < N && me != call.withhold_rank) st_release_sys_u64(rk.peer_gather_flags[tid] + slot * N + me, call.epoch);
 
     stamp(1);
-    // 3. wait for every rank's row (bounded)
-    if (tid < N) {
-        const uint64_t* flag = rk.peer_gather_flags[me] + slot * N + tid;
-        if (!wait_flag_ge(flag, call.epoch, call.timeout_ns)) atomicMax(&s_timeout_peer, tid);
+    // 3. collect every rank's row (bounded), expose the matrix, reduce. A thread owns one expert:
+    //    it first issues the loads of eight ranks' words together and only then looks at them,
+    //    so the common case (all rows already here) costs one memory round trip.
+    const uint64_t* gathered = rk.peer_gather[me] + static_cast<int64_t>(slot) * N * Lpad;
+    for (int i = tid; i < L; i += blockDim.x) {
+        int32_t total = 0;
+        for (int r0 = 0; r0 < N; r0 += 8) {
+            uint64_t w[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u < N) w[u] = ld_relaxed_sys_u64(gathered + static_cast<int64_t>(r0 + u) * Lpad + i);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u < N) {
+                    if (static_cast<uint32_t>(w[u] >> 32) != tag &&
+                        !wait_tagged_word(gathered + static_cast<int64_t>(r0 + u) * Lpad + i, tag, call.timeout_ns, w[u])) {
+                        atomicMax(&s_timeout_peer, r0 + u);
+                        w[u] = 0;
+                    }
+                    const int32_t v = static_cast<int32_t>(static_cast<uint32_t>(w[u]));
+                    rk.loads_per_rank[static_cast<int64_t>(r0 + u) * L + i] = v;
+                    total += v;
+                }
+            }
+        }
+        rk.global_loads[i] = total;
     }
+    __threadfence_block();
     __syncthreads();
     if (s_timeout_peer >= 0) {
         if (tid == 0) report_error(rk.status, UEP_DEV_TIMEOUT_GATHER, s_timeout_peer);
@@ -214,20 +243,6 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     }
 
     stamp(2);
-    // 4. reduce, expose the matrix, solve
-    const int32_t* gathered = rk.peer_gather[me] + static_cast<int64_t>(slot) * N * Lpad;
-    for (int i = tid; i < L; i += blockDim.x) {
-        int32_t total = 0;
-        for (int r = 0; r < N; ++r) {
-            const int32_t v = __ldcg(gathered + static_cast<int64_t>(r) * Lpad + i);
-            rk.loads_per_rank[static_cast<int64_t>(r) * L + i] = v;
-            total += v;
-        }
-        rk.global_loads[i] = total;
-    }
-    __threadfence_block();
-    __syncthreads();
-
     stamp(3);
     SolveArgs a;
     a.global_loads = rk.global_loads;

@@ -14,6 +14,8 @@
 //   * output arrays are cleared by the same CTA instead of six memsets.
 #pragma once
 
+#include <climits>
+
 #include "common.cuh"
 
 namespace uep {
@@ -49,7 +51,7 @@ constexpr int kSolverProbeWarps = 4;
 enum SolverCtrl {
     kCtlLo = 0, kCtlHi, kCtlPrecheckDone, kCtlFastDone, kCtlNumExports, kCtlSmallRange,
     kCtlProbe0, kCtlValid0 = kCtlProbe0 + kSolverProbeWarps, kCtlFeasible0 = kCtlValid0 + kSolverProbeWarps,
-    kCtlCount = kCtlFeasible0 + kSolverProbeWarps
+    kCtlMultiCount = kCtlFeasible0 + kSolverProbeWarps, kCtlCount
 };
 
 struct SolverSmem {
@@ -316,6 +318,79 @@ __device__ void build_rank_quota_prefix(const SolveArgs& a, int l_global, int C,
     }
 }
 
+__device__ __forceinline__ int warp_inclusive_scan(int v, int lane) {
+#pragma unroll
+    for (int off = 1; off < kWarp; off <<= 1) {
+        const int t = __shfl_up_sync(kFullMask, v, off);
+        if (lane >= off) v += t;
+    }
+    return v;
+}
+
+// The split of build_rank_quota_prefix for an expert with 2..32 replicas, by one warp: lane j
+// holds replica j, the sums and arg-max searches are warp reductions, and the hosts' own loads
+// are fetched by all lanes at once. Returns false (nothing written) when two replicas share a
+// host rank, which the sequential bookkeeping of the general version is needed for.
+__device__ __forceinline__ bool warp_rank_quota_prefix(const SolveArgs& a, int l_global, int C, int my_load, int phys,
+                                                       int q, int Lp, int L, int lane) {
+    const bool active = lane < C;
+    const int host = active ? phys / Lp : -1 - lane;
+    int my_alloc = 0;
+    if (!a.locality) {
+        const int total_quota = __reduce_add_sync(kFullMask, active ? q : 0);
+        if (my_load > 0 && total_quota > 0) {
+            const long long scaled = static_cast<long long>(my_load) * (active ? q : 0);
+            const int share = static_cast<int>(scaled / total_quota);
+            int rem = active ? static_cast<int>(scaled % total_quota) : INT_MIN;
+            my_alloc = share;
+            int remaining = my_load - __reduce_add_sync(kFullMask, share);  // < C: a sum of C fractional parts
+            for (int it = 0; it < C && remaining > 0; ++it) {
+                const int best = __reduce_max_sync(kFullMask, rem);
+                const int pick = __ffs(__ballot_sync(kFullMask, active && rem == best)) - 1;  // ties: the lower j
+                if (lane == pick) {
+                    my_alloc += 1;
+                    rem = -1;
+                }
+                --remaining;
+            }
+        }
+    } else {
+        const unsigned same_host = __match_any_sync(kFullMask, host);  // all 32 lanes take part: not under `active &&`
+        if (__any_sync(kFullMask, active && __popc(same_host) > 1)) return false;
+        const int own = active ? __ldcg(a.loads_per_rank + static_cast<int64_t>(host) * L + l_global) : 0;
+        const int local_fill = active ? min(own, q) : 0;
+        const int remote_cap = active ? q - local_fill : 0;
+        const int total_remote_cap = __reduce_add_sync(kFullMask, remote_cap);
+        const bool mine = active && host == a.my_rank;
+        if (mine) my_alloc = local_fill;
+        const int rem_my = max(my_load - __reduce_add_sync(kFullMask, mine ? local_fill : 0), 0);
+        if (rem_my > 0 && total_remote_cap > 0) {
+            const bool eligible = active && !mine && remote_cap > 0;
+            const long long scaled = static_cast<long long>(rem_my) * (eligible ? remote_cap : 0);
+            const int share = static_cast<int>(scaled / total_remote_cap);
+            int rem = eligible ? static_cast<int>(scaled % total_remote_cap) : INT_MIN;
+            my_alloc += share;
+            int remaining = rem_my - __reduce_add_sync(kFullMask, share);  // < number of eligible replicas
+            for (int it = 0; it < C && remaining > 0; ++it) {
+                const int best = __reduce_max_sync(kFullMask, rem);
+                if (best == INT_MIN) break;  // nobody can take a unit
+                // ties: the lower host rank, then the lower j
+                const bool cand = eligible && rem == best;
+                const int best_host = __reduce_min_sync(kFullMask, cand ? host : INT_MAX);
+                const int pick = __ffs(__ballot_sync(kFullMask, cand && host == best_host)) - 1;
+                if (lane == pick) {
+                    my_alloc += 1;
+                    rem = -1;
+                }
+                --remaining;
+            }
+        }
+    }
+    const int prefix = warp_inclusive_scan(my_alloc, lane);
+    if (active) a.rank_quota_prefix[static_cast<int64_t>(l_global) * a.D + lane] = prefix;
+    return true;
+}
+
 // Solve one NVLink domain. All threads of the CTA must call it (blockDim.x >= 128,
 // multiple of 32). smem_raw must hold solver_smem_bytes(E, G) bytes, 16-byte aligned.
 template <int NS>
@@ -533,80 +608,111 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
     }
 
     stamp(3);
-    // Emit: master quotas, then replicas in plan order.
+    // Emit: master quotas, then replicas in plan order. Two tables of the search are free by now
+    // and are reused: sorted_experts becomes "first plan entry of this expert" (an expert's
+    // exports are consecutive in the plan: they are all made while its one source rank is being
+    // drained), and the probe warps' scratch becomes the list of experts that have replicas.
+    int* first_entry = sm.sorted_experts;
+    int* multi_list = sm.export_sum + E;
     for (int e = tid; e < E; e += nthreads) {
         const int64_t row = static_cast<int64_t>(domain_start_log + e) * D;
         a.quota[row] = do_search ? (sm.loads[e] - sm.export_sum[e]) : sm.loads[e];
     }
+    if (tid == 0) sm.ctrl[kCtlMultiCount] = 0;
     __syncthreads();
-    if (tid == 0) {
+    if (warp == 0) {
+        // 32 plan entries at a time: an entry's replica slot (and its target's redundant slot) is
+        // the counter left by the earlier chunks plus the number of lower lanes that name the same
+        // expert (the same target), which is exactly the creation order of a serial walk.
         const int n = sm.ctrl[kCtlNumExports];
-        for (int k = 0; k < n; ++k) {
-            const ExportEntry entry = sm.plan[k];
-            const int l_global = domain_start_log + entry.expert_local;
-            const int64_t row = static_cast<int64_t>(l_global) * D;
-            const int slot = sm.expert_slot[entry.expert_local]++;
-            const int phys =
-                (domain_start_rank + entry.target_rank_local) * Lp + M + sm.next_slot[entry.target_rank_local]++;
-            if (slot >= D || phys >= (domain_start_rank + entry.target_rank_local + 1) * Lp) {
-                report_error(status, UEP_DEV_BAD_PLAN, k);
-                continue;
+        for (int base = 0; base < n; base += kWarp) {
+            const int k = base + lane;
+            const bool active = k < n;
+            const unsigned amask = __ballot_sync(kFullMask, active);
+            if (active) {
+                const ExportEntry entry = sm.plan[k];
+                const unsigned same_e = __match_any_sync(amask, entry.expert_local);
+                const unsigned same_t = __match_any_sync(amask, entry.target_rank_local);
+                const unsigned below = (1u << lane) - 1u;
+                const int slot = sm.expert_slot[entry.expert_local] + __popc(same_e & below);
+                const int tslot = sm.next_slot[entry.target_rank_local] + __popc(same_t & below);
+                __syncwarp(amask);  // every lane has read the counters
+                if ((same_e >> lane) == 1u) sm.expert_slot[entry.expert_local] = slot + 1;  // highest lane of its group
+                if ((same_t >> lane) == 1u) sm.next_slot[entry.target_rank_local] = tslot + 1;
+                if (slot == 1) first_entry[entry.expert_local] = k;
+                const int l_global = domain_start_log + entry.expert_local;
+                const int64_t row = static_cast<int64_t>(l_global) * D;
+                const int phys = (domain_start_rank + entry.target_rank_local) * Lp + M + tslot;
+                if (slot >= D || phys >= (domain_start_rank + entry.target_rank_local + 1) * Lp) {
+                    report_error(status, UEP_DEV_BAD_PLAN, k);
+                } else {
+                    a.p2l[phys] = l_global;
+                    a.l2p[row + slot] = phys;
+                    a.quota[row + slot] = entry.quota;
+                    sm.plan[k].target_rank_local = phys;  // from here on the entry carries the physical id
+                }
             }
-            a.p2l[phys] = l_global;
-            a.l2p[row + slot] = phys;
-            a.quota[row + slot] = entry.quota;
-            sm.plan[k].target_rank_local = phys;  // from here on the entry carries the physical id
+            __syncwarp();
         }
     }
     __syncthreads();
     stamp(4);
-    const int n_exports = sm.ctrl[kCtlNumExports];
+    // Counts and prefixes. An expert without replicas keeps all of this rank's tokens (every
+    // branch of the split reduces to that), so one thread writes its row; the others go to the
+    // warps, one expert per warp at a time.
     for (int e = tid; e < E; e += nthreads) {
         const int l_global = domain_start_log + e;
         const int64_t row = static_cast<int64_t>(l_global) * D;
         const int C = min(sm.expert_slot[e], D);
         a.lcnts[l_global] = C;
-        const int master_quota = do_search ? (sm.loads[e] - sm.export_sum[e]) : sm.loads[e];
-        const int master_phys = (domain_start_rank + e / M) * Lp + e % M;
-        if (C <= 8) {
-            int phys[8], q[8];
-            phys[0] = master_phys;
-            q[0] = master_quota;
-            int j = 1;
-            if (C > 1) {
-                for (int k = 0; k < n_exports && j < C; ++k) {
-                    if (sm.plan[k].expert_local == e) {
-                        phys[j] = sm.plan[k].target_rank_local;
-                        q[j] = sm.plan[k].quota;
-                        ++j;
-                    }
-                }
-            }
-            int prefix = 0;
-            for (int jj = 0; jj < C; ++jj) {
-                prefix += q[jj];
-                a.quota_prefix[row + jj] = prefix;
-            }
-            build_rank_quota_prefix<8>(a, l_global, C, sm.my_loads[e], phys, q, Lp, L);
+        if (C == 1) {
+            a.quota_prefix[row] = do_search ? (sm.loads[e] - sm.export_sum[e]) : sm.loads[e];
+            a.rank_quota_prefix[row] = sm.my_loads[e];
         } else {
+            multi_list[atomicAdd(&sm.ctrl[kCtlMultiCount], 1)] = e;
+        }
+    }
+    __syncthreads();
+    const int n_multi = sm.ctrl[kCtlMultiCount];
+    for (int idx = warp; idx < n_multi; idx += nthreads / kWarp) {
+        const int e = multi_list[idx];
+        const int l_global = domain_start_log + e;
+        const int64_t row = static_cast<int64_t>(l_global) * D;
+        const int C = min(sm.expert_slot[e], D);
+        const int master_quota = sm.loads[e] - sm.export_sum[e];
+        const int master_phys = (domain_start_rank + e / M) * Lp + e % M;
+        const int first = first_entry[e];
+        bool done = false;
+        if (C <= kWarp) {
+            int phys = 0, q = 0;
+            if (lane == 0) {
+                phys = master_phys;
+                q = master_quota;
+            } else if (lane < C) {
+                const ExportEntry entry = sm.plan[first + lane - 1];
+                phys = entry.target_rank_local;
+                q = entry.quota;
+            }
+            const int qp = warp_inclusive_scan(q, lane);
+            if (lane < C) a.quota_prefix[row + lane] = qp;
+            done = warp_rank_quota_prefix(a, l_global, C, sm.my_loads[e], phys, q, Lp, L, lane);
+        }
+        if (!done && lane == 0) {  // more than 32 replicas, or two replicas on one rank: the serial version
             int phys[kMaxRanksPerDomain], q[kMaxRanksPerDomain];
             phys[0] = master_phys;
             q[0] = master_quota;
-            int j = 1;
-            for (int k = 0; k < n_exports && j < C; ++k) {
-                if (sm.plan[k].expert_local == e) {
-                    phys[j] = sm.plan[k].target_rank_local;
-                    q[j] = sm.plan[k].quota;
-                    ++j;
-                }
-            }
             int prefix = 0;
-            for (int jj = 0; jj < C; ++jj) {
-                prefix += q[jj];
-                a.quota_prefix[row + jj] = prefix;
+            for (int j = 0; j < C; ++j) {
+                if (j > 0) {
+                    phys[j] = sm.plan[first + j - 1].target_rank_local;
+                    q[j] = sm.plan[first + j - 1].quota;
+                }
+                prefix += q[j];
+                a.quota_prefix[row + j] = prefix;
             }
             build_rank_quota_prefix<kMaxRanksPerDomain>(a, l_global, C, sm.my_loads[e], phys, q, Lp, L);
         }
+        __syncwarp();
     }
     __syncthreads();
     stamp(5);
