@@ -165,19 +165,20 @@ class ForwardWorkload:
         self.flush.zero_()
         self.flush_read.sum()
 
-    def step(self, i, ids=None):
+    def step(self, i, ids=None, result_to_host=False):
         g = self.group
         layer = i % self.num_layers
         ids = self.ids_dev[i % len(self.ids_dev)] if ids is None else ids
         g.update_placement(layer, ids)
         ev = g.weight_sync(layer, self.tables[0], self.tables[1], self.tables[2], self.tables[3], async_finish=True)
         g.reroute_sparse(layer, ids, self.phys_dev)
+        if result_to_host:  # the physical ids leave while the weights are still in flight
+            self.phys_host.copy_(self.phys_all, non_blocking=True)
         g.wait_event(ev)
 
     def step_e2e(self, i):
         self.stage_all.copy_(self.ids_host[i % len(self.ids_host)], non_blocking=True)
-        self.step(i, self.ids_stage)
-        self.phys_host.copy_(self.phys_all, non_blocking=True)
+        self.step(i, self.ids_stage, result_to_host=True)
 
     def sync_bytes(self, layer):
         """Algorithmic bytes of one weight_sync launch of the hosted ranks: every replicated

@@ -47,6 +47,10 @@ struct SyncShared {
     const uint8_t* src[kMaxExpertsPerDomain][4];  // [n_active][shard] master shard base
     uint8_t* dst_weight[kMaxSends];               // replica slot base in the peer's weight buffer (null: skip)
     uint8_t* dst_scale[kMaxSends];                // replica slot base in the peer's scale buffer
+    // replica buffer bases of every (hosted rank, peer): nlocal * N entries (at most 72: several
+    // hosted ranks mean a simulated group of at most 8)
+    uint8_t* peer_weight[kMaxPeers];
+    uint8_t* peer_scale[kMaxPeers];
 };
 
 struct TileRef {
@@ -121,8 +125,44 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         sm.recv_mask[i / 3][i % 3] = 0;
     }
     __syncthreads();
-    // blocked scan over (hosted rank, master): active index and replica offsets
+    // Every global read of the set-up is issued here, before anything depends on one of them, so
+    // that they share one memory round trip instead of forming a chain (counts -> l2p rows ->
+    // peer tables): the plan rows of the first 128 masters (speculatively the whole l2p row when
+    // it has at most 8 entries), their source addresses, the peers' buffer bases and the
+    // owners of this rank's redundant slots.
     const int total_masters = nlocal * M;
+    const bool row_cached = D <= 8;
+    int pre_reps = 0, pre_row[7];
+    uintptr_t pre_src[4];
+    {
+        const bool valid = tid < total_masters;
+        const int lr = valid ? tid / M : 0, m = valid ? tid % M : 0;
+        const int l = call.my_rank[lr] * M + m;
+        const PlanPtrs& plan = call.plan[lr];
+        pre_reps = valid ? plan.lcnts[l] - 1 : 0;
+#pragma unroll
+        for (int j = 0; j < 7; ++j) pre_row[j] = (valid && row_cached && j < D - 1) ? plan.l2p[static_cast<int64_t>(l) * D + 1 + j] : -1;
+#pragma unroll
+        for (int sh_i = 0; sh_i < 4; ++sh_i) {
+            const bool present = valid && sh_i < sh.num_shards && sh.bytes[sh_i] != 0;
+            pre_src[sh_i] = present ? static_cast<uintptr_t>(call.src_ptrs[lr][sh_i][m]) : 0;
+        }
+    }
+    uint8_t *pre_pw = nullptr, *pre_ps = nullptr;
+    if (tid < nlocal * N) {
+        const RankDev& rk = *call.rank[tid / N];
+        pre_pw = rk.peer_replica_weight[tid % N];
+        pre_ps = rk.peer_replica_scale[tid % N];
+    }
+    int pre_owner = -1;
+    if (tid < nlocal * R) pre_owner = call.plan[tid / R].p2l[call.my_rank[tid / R] * Lp + M + tid % R];
+    if (tid < nlocal * N) {
+        sm.peer_weight[tid] = pre_pw;
+        sm.peer_scale[tid] = pre_ps;
+    }
+    // (the scan below synchronises the CTA before the tables are read)
+
+    // blocked scan over (hosted rank, master): active index and replica offsets
     for (int g0 = 0; g0 < total_masters; g0 += blockDim.x) {
         const int gm = g0 + tid;
         const int lr = gm < total_masters ? gm / M : 0;
@@ -132,7 +172,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         const int me = call.my_rank[lr];
         int reps = 0;
         if (gm < total_masters) {
-            reps = plan.lcnts[me * M + m] - 1;
+            reps = g0 == 0 ? pre_reps : plan.lcnts[me * M + m] - 1;
             reps = reps < 0 ? 0 : (reps > D - 1 ? D - 1 : reps);
         }
         const int act = reps > 0 ? 1 : 0;
@@ -163,8 +203,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             const int rs = r_off + r_incl - reps;
             sm.rep_start[ai] = static_cast<short>(rs);
             const int l = me * M + m;
-            for (int j = 0; j < reps && rs + j < kMaxSends; ++j) {
-                const int phys = plan.l2p[static_cast<int64_t>(l) * D + 1 + j];
+            auto place = [&](int j, int phys) {
                 const int drank = phys / Lp, dslot = phys % Lp - M;
                 if (phys < 0 || drank >= N || dslot < 0 || dslot >= R) {  // never store outside a slot table
                     report_error(rk.status, UEP_DEV_BAD_PLAN, l);
@@ -172,14 +211,28 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                     sm.dst_scale[rs + j] = nullptr;
                 } else {
                     atomicOr(&sm.send_mask[lr][drank >> 5], 1u << (drank & 31));
-                    sm.dst_weight[rs + j] = rk.peer_replica_weight[drank] + static_cast<int64_t>(dslot) * sh.weight_slot_stride;
-                    sm.dst_scale[rs + j] = rk.peer_replica_scale[drank] + static_cast<int64_t>(dslot) * sh.scale_slot_stride;
+                    sm.dst_weight[rs + j] = sm.peer_weight[lr * N + drank] + static_cast<int64_t>(dslot) * sh.weight_slot_stride;
+                    sm.dst_scale[rs + j] = sm.peer_scale[lr * N + drank] + static_cast<int64_t>(dslot) * sh.scale_slot_stride;
                 }
+            };
+            if (g0 == 0 && row_cached) {
+#pragma unroll
+                for (int j = 0; j < 7; ++j) {
+                    if (j < reps && rs + j < kMaxSends) place(j, pre_row[j]);
+                }
+            } else {
+                for (int j = 0; j < reps && rs + j < kMaxSends; ++j) place(j, plan.l2p[static_cast<int64_t>(l) * D + 1 + j]);
             }
             // source addresses and their alignment
             for (int s = 0; s < 4; ++s) {
                 const bool present = s < sh.num_shards && sh.bytes[s] != 0;
-                const uintptr_t p = present ? static_cast<uintptr_t>(call.src_ptrs[lr][s][m]) : 0;
+                uintptr_t p = 0;
+                if (g0 == 0) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) p = (u == s) ? pre_src[u] : p;
+                } else if (present) {
+                    p = static_cast<uintptr_t>(call.src_ptrs[lr][s][m]);
+                }
                 sm.src[ai][s] = reinterpret_cast<const uint8_t*>(p);
                 if (p & 15u) atomicAnd(&sm.all_aligned, 0);
             }
@@ -195,7 +248,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     for (int i = tid; i < nlocal * R; i += blockDim.x) {
         const int lr = i / R, slot = i % R;
         const int me = call.my_rank[lr];
-        const int l = call.plan[lr].p2l[me * Lp + M + slot];
+        const int l = i == tid ? pre_owner : call.plan[lr].p2l[me * Lp + M + slot];
         if (l >= 0) {
             const int src = l / M;
             if (src >= 0 && src < N && src != me) atomicOr(&sm.recv_mask[lr][src >> 5], 1u << (src & 31));
