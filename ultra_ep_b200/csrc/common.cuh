@@ -101,6 +101,20 @@ __device__ __forceinline__ bool wait_tagged_word(const uint64_t* p, uint32_t tag
     }
 }
 
+// As wait_flag_ge, with relaxed polls: the caller closes the wait with one acquire fence.
+__device__ __forceinline__ bool wait_flag_ge_relaxed(const uint64_t* flag, uint64_t target, uint64_t timeout_ns) {
+    if (ld_relaxed_sys_u64(flag) >= target) return true;
+    const uint64_t start = global_timer_ns();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            if (ld_relaxed_sys_u64(flag) >= target) return true;
+            __nanosleep(20);
+        }
+        if (global_timer_ns() - start > timeout_ns) return false;
+    }
+}
+
 // ---------------------------------------------------------------------------------
 // mbarrier + bulk async copies (non-multicast, 1-D). Addresses and sizes must be
 // multiples of 16 bytes; callers check and take a plain-load path otherwise.

@@ -375,25 +375,40 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     __syncthreads();
     stamp(5);
     if (!sm.is_last) return;
-    for (int i = tid; i < nlocal * N; i += blockDim.x) {
-        const int lr = i / N, p = i % N;
-        const RankDev& rk = *call.rank[lr];
-        if ((sm.send_mask[lr][p >> 5] & (1u << (p & 31))) && rk.my_rank != call.withhold_rank) {
-            st_release_sys_u64(rk.peer_sync_flags[p] + rk.my_rank, call.epoch);
-        }
-    }
-    __syncthreads();
-    for (int i = tid; i < nlocal * N; i += blockDim.x) {
-        const int lr = i / N, p = i % N;
-        const RankDev& rk = *call.rank[lr];
-        if (sm.recv_mask[lr][p >> 5] & (1u << (p & 31))) {
-            if (!wait_flag_ge(rk.peer_sync_flags[rk.my_rank] + p, call.epoch, call.timeout_ns)) {
-                atomicMax(&sm.timeout_peer, p);
-                report_error(rk.status, UEP_DEV_TIMEOUT_SYNC, p);
+    // Every CTA's copies are complete and ordered before this point (fence + ticket above).
+    // Ranks hosted by this very launch need no flag at all: the ticket is their proof. Towards
+    // ranks on other devices one thread issues a single system-scope fence and then the flags
+    // (a fence followed by relaxed stores is a release of everything observed so far); the
+    // waits are relaxed polls closed by one acquire fence. The test hook that withholds a rank
+    // forces the flags between hosted ranks too, so that the time-out path can be exercised on
+    // one device.
+    const bool flags_needed = nlocal == 1 || call.withhold_rank >= 0;
+    if (flags_needed) {
+        if (tid == 0) {
+            __threadfence_system();
+            for (int lr = 0; lr < nlocal; ++lr) {
+                const int me = call.my_rank[lr];
+                if (me == call.withhold_rank) continue;
+                const RankDev& rk = *call.rank[lr];
+                for (int p = 0; p < N; ++p) {
+                    if (sm.send_mask[lr][p >> 5] & (1u << (p & 31))) st_relaxed_sys_u64(rk.peer_sync_flags[p] + me, call.epoch);
+                }
             }
         }
+        stamp(7);
+        for (int i = tid; i < nlocal * N; i += blockDim.x) {
+            const int lr = i / N, p = i % N;
+            if (sm.recv_mask[lr][p >> 5] & (1u << (p & 31))) {
+                const RankDev& rk = *call.rank[lr];
+                if (!wait_flag_ge_relaxed(rk.peer_sync_flags[call.my_rank[lr]] + p, call.epoch, call.timeout_ns)) {
+                    atomicMax(&sm.timeout_peer, p);
+                    report_error(rk.status, UEP_DEV_TIMEOUT_SYNC, p);
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) __threadfence_system();  // acquire side of the flags seen by the polls above
     }
-    __syncthreads();
     stamp(6);
 }
 
