@@ -9,15 +9,16 @@
 // replica sub-tile at a time through a single shared-memory buffer (load, wait, add, zero
 // with per-thread stores, repeat). Here:
 //   * no task list: every CTA derives the pull list from the plan rows with a block scan;
-//   * accumulators live in registers (8 floats per thread per 8 KiB tile);
-//   * an elected thread keeps a 6-stage ring of bulk loads from peer memory in flight, so
-//     the NVLink latency of replica j+1 .. j+5 (and of the next tiles) is hidden behind the
-//     add of replica j;
+//   * accumulators live in registers (16 floats per thread per 16 KiB tile);
+//   * an elected thread keeps a 7-stage ring of 16 KiB bulk loads in flight; the master tile
+//     travels through the same ring in front of its replicas, so no thread ever waits on a
+//     plain global load, and the 112 KiB per CTA (4.7 MB over the default 42 CTAs) cover the
+//     bandwidth-delay product of an NVLink read (about 770 GB/s x 3.5 us);
 //   * the consumed region is zeroed with one bulk store from a zero-filled shared buffer
 //     instead of 256 threads of vector stores;
 //   * tiles are interleaved over masters so that concurrent CTAs pull from different peers.
-// The CTA budget (SMs used while the backward pass runs next to it) and the 56 KiB of
-// shared memory per CTA keep room for compute kernels on the same SMs.
+// The CTA budget (SMs used while the backward pass runs next to it) is the caller's knob
+// (grad_reduce_num_sms); each CTA holds 128 KiB of shared memory.
 
 #include "internal.h"
 
@@ -26,9 +27,10 @@ namespace uep {
 namespace {
 
 constexpr int kReduceThreads = 256;
-constexpr int kReduceTileElems = 2048;  // 8 KiB
+constexpr int kReduceTileElems = 4096;  // 16 KiB
 constexpr int kReduceTileBytes = kReduceTileElems * 4;
-constexpr int kReduceStages = 6;
+constexpr int kReduceStages = 7;
+constexpr int kReduceVecPerThread = kReduceTileElems / 4 / kReduceThreads;  // float4 per thread per tile
 constexpr int kMaxPulls = kMaxExportsPerDomain;
 
 struct ReduceShared {
@@ -184,10 +186,17 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
     }
 
     // ---- pipelined path -----------------------------------------------------------------
-    // producer cursor (thread 0): next (item, replica) pair whose load has not been issued
+    // producer cursor (thread 0): the loads of one item are its master tile, then its replicas
     int64_t prod_k = 0;
-    int prod_r = -1, prod_r_end = -1;
+    int prod_r = -1, prod_r_end = -1;  // prod_r < 0: the master tile of item prod_k is next
     int64_t issued = 0;
+    auto issue = [&](const float* src, int elems) {
+        const int s = static_cast<int>(issued % kReduceStages);
+        const uint32_t bytes = static_cast<uint32_t>(elems) * 4u;
+        mbar_expect_tx(&bars[s], bytes);
+        bulk_load(smem_raw + s * kReduceTileBytes, src, bytes, &bars[s]);
+        ++issued;
+    };
     auto produce_one = [&]() -> bool {  // thread 0 only; false when nothing is left
         while (true) {
             if (prod_k >= count) return false;
@@ -195,6 +204,8 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
             if (prod_r < 0) {
                 prod_r = sm.rep_start[it.active];
                 prod_r_end = sm.rep_start[it.active + 1];
+                issue(master_ptr(it), it.elems);
+                return true;
             }
             while (prod_r < prod_r_end && sm.rep_base[prod_r] == nullptr) ++prod_r;
             if (prod_r >= prod_r_end) {
@@ -202,11 +213,7 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
                 prod_r = -1;
                 continue;
             }
-            const int s = static_cast<int>(issued % kReduceStages);
-            const uint32_t bytes = static_cast<uint32_t>(it.elems) * 4u;
-            mbar_expect_tx(&bars[s], bytes);
-            bulk_load(smem_raw + s * kReduceTileBytes, replica_ptr(it, prod_r), bytes, &bars[s]);
-            ++issued;
+            issue(replica_ptr(it, prod_r), it.elems);
             ++prod_r;
             return true;
         }
@@ -217,31 +224,41 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
         }
     }
     int64_t consumed = 0;
+    auto wait_stage = [&]() -> const float4* {
+        const int s = static_cast<int>(consumed % kReduceStages);
+        if (!mbar_wait(&bars[s], static_cast<uint32_t>((consumed / kReduceStages) & 1), call.timeout_ns)) {
+            sm.error = 1;  // keep the control flow uniform; the result of this tile is void
+        }
+        return reinterpret_cast<const float4*>(smem_raw + s * kReduceTileBytes);
+    };
     for (int64_t k = 0; k < count; ++k) {
         const ReduceItem it = decode_item(first + k * step, sm.n_active, fc1, fc2, tiles_fc1);
         float4* mp = reinterpret_cast<float4*>(master_ptr(it));
         const int nvec = it.elems >> 2;
-        const bool has0 = tid < nvec, has1 = tid + kReduceThreads < nvec;
-        float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
-        if (has0) acc0 = mp[tid];
-        if (has1) acc1 = mp[tid + kReduceThreads];
+        float4 acc[kReduceVecPerThread];
+        {
+            const float4* stage = wait_stage();
+#pragma unroll
+            for (int u = 0; u < kReduceVecPerThread; ++u) {
+                const int i = tid + u * kReduceThreads;
+                acc[u] = i < nvec ? stage[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            ++consumed;
+            __syncthreads();  // the stage is free again
+            if (tid == 0) produce_one();
+        }
         const int r0 = sm.rep_start[it.active], r1 = sm.rep_start[it.active + 1];
         for (int r = r0; r < r1; ++r) {
             if (sm.rep_base[r] == nullptr) continue;
-            const int s = static_cast<int>(consumed % kReduceStages);
-            if (!mbar_wait(&bars[s], static_cast<uint32_t>((consumed / kReduceStages) & 1), call.timeout_ns)) {
-                sm.error = 1;  // keep the control flow uniform; the result of this tile is void
-            }
-            const float4* stage = reinterpret_cast<const float4*>(smem_raw + s * kReduceTileBytes);
-            if (has0) {
-                const float4 v = stage[tid];
-                acc0.x = __fadd_rn(acc0.x, v.x); acc0.y = __fadd_rn(acc0.y, v.y);
-                acc0.z = __fadd_rn(acc0.z, v.z); acc0.w = __fadd_rn(acc0.w, v.w);
-            }
-            if (has1) {
-                const float4 v = stage[tid + kReduceThreads];
-                acc1.x = __fadd_rn(acc1.x, v.x); acc1.y = __fadd_rn(acc1.y, v.y);
-                acc1.z = __fadd_rn(acc1.z, v.z); acc1.w = __fadd_rn(acc1.w, v.w);
+            const float4* stage = wait_stage();
+#pragma unroll
+            for (int u = 0; u < kReduceVecPerThread; ++u) {
+                const int i = tid + u * kReduceThreads;
+                if (i < nvec) {
+                    const float4 v = stage[i];
+                    acc[u].x = __fadd_rn(acc[u].x, v.x); acc[u].y = __fadd_rn(acc[u].y, v.y);
+                    acc[u].z = __fadd_rn(acc[u].z, v.z); acc[u].w = __fadd_rn(acc[u].w, v.w);
+                }
             }
             ++consumed;
             __syncthreads();  // the stage is free again
@@ -251,8 +268,11 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
                 produce_one();
             }
         }
-        if (has0) mp[tid] = acc0;
-        if (has1) mp[tid + kReduceThreads] = acc1;
+#pragma unroll
+        for (int u = 0; u < kReduceVecPerThread; ++u) {
+            const int i = tid + u * kReduceThreads;
+            if (i < nvec) mp[i] = acc[u];
+        }
     }
     if (tid == 0) {
         bulk_wait_all<0>();

@@ -561,7 +561,8 @@ int uep_grad_reduce(uep_manager* m, int layer_id, const int64_t* const* fc1_grad
     call.fc1_numel = m->cfg.expert_fc1_numel;
     call.fc2_numel = m->cfg.expert_fc2_numel;
     call.timeout_ns = m->timeout_ns;
-    call.ctas_per_rank = m->grad_reduce_ctas;
+    // one CTA per SM at most (128 KiB of shared memory each): hosted ranks share the device's SMs
+    call.ctas_per_rank = std::max(1, std::min(m->grad_reduce_ctas, m->num_sms / m->nlocal));
     if (m->R > 0 && m->total_numel > 0) UEP_CUDA_TRY(launch_grad_reduce(call, m->comm_stream));
     return finish_sync_op(m, async_finish, current, done_event);
 }
