@@ -57,6 +57,10 @@ def load_peaks():
 
 
 NVLINK_PEER_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool (nominal 900)
+# DRAM bytes moved inside a full-size weight_sync launch / its algorithmic bytes, from the one-pass ncu capture
+# summarised in profiles/weight_sync_kernel_cfg3_dram_traffic.md (reads match; part of the writes is still dirty
+# in L2 when the kernel ends)
+NCU_SYNC_TRAFFIC_RATIO = 0.72
 
 
 class ClockSampler:
@@ -348,7 +352,10 @@ def run_ours(args):
         alg_bytes = (rd + wr) / nb
         achieved = (rd + wr) / 1e9 / (sync_total_ms / 1e3)
         roofline = {"kernel": "weight_sync_kernel", "bound": "hbm", "achieved": round(achieved, 1), "peak": peak_hbm,
-                    "unit": "GB/s", "frac": round(achieved / peak_hbm, 4), "traffic": None,
+                    "unit": "GB/s", "frac": round(achieved / peak_hbm, 4),
+                    "traffic": int(alg_bytes * NCU_SYNC_TRAFFIC_RATIO) if base.name == "cfg3_qwen3_235b_fp8" else None,
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a full-size launch, as a "
+                                      "ratio of its algorithmic bytes (profiles/weight_sync_kernel_cfg3_dram_traffic.md)",
                     "algorithmic_bytes_per_launch": int(alg_bytes), "peak_source": peak_src + "; of measured",
                     "note": "simulated EP: peers are same-device buffers, bytes = reads + writes through HBM"}
     else:
