@@ -32,6 +32,9 @@ struct RankDev {
     float* peer_replica_grad[kMaxPeers];
     uint64_t* peer_sync_flags[kMaxPeers];  // each: [N], entry [src] = last epoch src finished sending to that rank
     DeviceStatus* status;    // mapped pinned host memory
+    // [0] plan epoch, [1] sync epoch: counted on the device (by the CTA that finishes a launch), not
+    // passed by value, so that a captured CUDA graph can be replayed: every replay is a new epoch
+    uint64_t* epochs;
 };
 
 struct PlanPtrs {
@@ -58,7 +61,6 @@ struct PlanCall {
     int K_or_L;
     int N, G, M, R, D;
     uep_solver_params params;
-    uint64_t epoch;
     uint64_t timeout_ns;
     int ctas_per_rank;
     int withhold_rank;  // test hook: this rank does not publish its flags (-1: none)
@@ -75,7 +77,6 @@ struct SyncCall {
     int nlocal;
     int N, M, R, D;
     ShardLayout shards;
-    uint64_t epoch;
     uint64_t timeout_ns;
     int ctas_per_rank;
     int withhold_rank;  // test hook, as in PlanCall

@@ -40,6 +40,7 @@ struct RankHost {
     int32_t* rank_quota_prefix = nullptr;       // [layers][L][D]
     int32_t* local_hist = nullptr;              // [Lpad]
     int* tickets = nullptr;                     // [4]: plan ticket, sync ticket, sync tile counter, spare
+    uint64_t* epochs = nullptr;                 // [2]: plan epoch, sync epoch (device-counted)
     int32_t* global_loads = nullptr;            // [L]
     int32_t* loads_per_rank = nullptr;          // [N][L]
     DeviceStatus* status_host = nullptr;        // mapped pinned
@@ -67,7 +68,6 @@ struct uep_manager {
     std::vector<cudaEvent_t> plan_ready;
     std::vector<cudaStream_t> plan_stream;
     std::vector<char> plan_recorded;
-    uint64_t plan_epoch = 0, sync_epoch = 0;
     uint64_t timeout_ns = 0;
     bool connected = false;
     int grad_reduce_ctas = 42;
@@ -137,6 +137,7 @@ int upload_rank_dev(uep_manager* m, RankHost& r) {
     d.local_hist = r.local_hist;
     d.plan_ticket = r.tickets;
     d.sync_ticket = r.tickets + 1;
+    d.epochs = r.epochs;
     d.global_loads = r.global_loads;
     d.loads_per_rank = r.loads_per_rank;
     d.status = r.status_dev;
@@ -165,6 +166,7 @@ void free_rank(RankHost& r, int my_rank_count) {
     cudaFree(r.rank_quota_prefix);
     cudaFree(r.local_hist);
     cudaFree(r.tickets);
+    cudaFree(r.epochs);
     cudaFree(r.global_loads);
     cudaFree(r.loads_per_rank);
     cudaFree(r.dev);
@@ -312,6 +314,8 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
         UEP_TRY_BAIL(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
         UEP_TRY_BAIL(cudaMalloc(&r.tickets, sizeof(int) * 4));
         UEP_TRY_BAIL(cudaMemset(r.tickets, 0, sizeof(int) * 4));
+        UEP_TRY_BAIL(cudaMalloc(&r.epochs, sizeof(uint64_t) * 2));
+        UEP_TRY_BAIL(cudaMemset(r.epochs, 0, sizeof(uint64_t) * 2));
         UEP_TRY_BAIL(cudaMalloc(&r.global_loads, sizeof(int32_t) * m->L));
         UEP_TRY_BAIL(cudaMemset(r.global_loads, 0, sizeof(int32_t) * m->L));
         UEP_TRY_BAIL(cudaMalloc(&r.loads_per_rank, sizeof(int32_t) * static_cast<size_t>(N) * m->L));
@@ -470,7 +474,6 @@ int uep_update_placement(uep_manager* m, int layer_id, int input_kind, const voi
     call.K_or_L = K_or_L;
     call.N = m->N; call.G = m->G; call.M = m->M; call.R = m->R; call.D = m->D;
     call.params = m->cfg.solver;
-    call.epoch = ++m->plan_epoch;
     call.timeout_ns = m->timeout_ns;
     call.ctas_per_rank = plan_ctas_per_rank(input_kind, max_T, K_or_L, m->nlocal, m->num_sms);
     call.withhold_rank = m->withhold_rank;
@@ -523,7 +526,6 @@ int uep_weight_sync(uep_manager* m, int layer_id, const int64_t* const* fc1_ptrs
     sh.slot_offset[0] = 0; sh.slot_offset[1] = m->fc1_bytes; sh.slot_offset[2] = 0; sh.slot_offset[3] = m->scale_fc2_offset;
     sh.weight_slot_stride = m->weight_stride;
     sh.scale_slot_stride = m->scale_stride;
-    call.epoch = ++m->sync_epoch;
     call.timeout_ns = m->timeout_ns;
     call.ctas_per_rank = m->weight_sync_ctas;
     call.withhold_rank = m->withhold_rank;

@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     extern __shared__ __align__(128) char smem_raw[];
     __shared__ int s_is_last;
     __shared__ int s_timeout_peer;
+    __shared__ uint64_t s_epoch;
 
     const int local = blockIdx.x / call.ctas_per_rank;
     const int part = blockIdx.x % call.ctas_per_rank;
@@ -176,6 +177,10 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
         const int ticket = atomicAdd(rk.plan_ticket, 1);
         s_is_last = (ticket == call.ctas_per_rank - 1) ? 1 : 0;
         s_timeout_peer = -1;
+        if (s_is_last) {  // one CTA per rank and launch gets here: it opens the next epoch
+            s_epoch = rk.epochs[0] + 1;
+            rk.epochs[0] = s_epoch;
+        }
     }
     __syncthreads();
     if (!s_is_last) return;
@@ -189,8 +194,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     // 2. the last CTA publishes the row to every rank (itself included) and resets the scratch.
     //    Every 64-bit word carries the epoch beside its count, so a row needs neither a fence nor
     //    a flag: one NVLink crossing, and the reader knows a word is this layer's when it sees it.
-    const int slot = static_cast<int>(call.epoch & 1ull);
-    const uint32_t tag = static_cast<uint32_t>(call.epoch);
+    const uint64_t epoch = s_epoch;
+    const int slot = static_cast<int>(epoch & 1ull);
+    const uint32_t tag = static_cast<uint32_t>(epoch);
     const int me = rk.my_rank;
     for (int i = tid; i < L; i += blockDim.x) {
         hist[i] = __ldcg(rk.local_hist + i);

@@ -41,6 +41,7 @@ struct SyncShared {
     unsigned send_mask[kMaxLocalRanks][3];  // per hosted rank: ranks it sends to
     unsigned recv_mask[kMaxLocalRanks][3];  // per hosted rank: ranks that send to it
     int timeout_peer;
+    unsigned long long epoch;  // opened by the last CTA of the launch
     short rep_start[kMaxExpertsPerDomain + 1];  // [n_active+1] offsets into dst_*
     // Addresses are resolved once per CTA: the issuing thread must not chase pointers
     // through global memory for every 32 KiB tile.
@@ -370,6 +371,9 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             *ticket_ptr = 0;
             *tile_counter = 0;  // every CTA has stopped taking tiles
             sm.is_last = 1;
+            // ranks hosted together share the first one's counter: they always run in the same launches
+            sm.epoch = call.rank[0]->epochs[1] + 1;
+            call.rank[0]->epochs[1] = sm.epoch;
         }
     }
     __syncthreads();
@@ -391,7 +395,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                 if (me == call.withhold_rank) continue;
                 const RankDev& rk = *call.rank[lr];
                 for (int p = 0; p < N; ++p) {
-                    if (sm.send_mask[lr][p >> 5] & (1u << (p & 31))) st_relaxed_sys_u64(rk.peer_sync_flags[p] + me, call.epoch);
+                    if (sm.send_mask[lr][p >> 5] & (1u << (p & 31))) st_relaxed_sys_u64(rk.peer_sync_flags[p] + me, sm.epoch);
                 }
             }
         }
@@ -400,7 +404,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             const int lr = i / N, p = i % N;
             if (sm.recv_mask[lr][p >> 5] & (1u << (p & 31))) {
                 const RankDev& rk = *call.rank[lr];
-                if (!wait_flag_ge_relaxed(rk.peer_sync_flags[call.my_rank[lr]] + p, call.epoch, call.timeout_ns)) {
+                if (!wait_flag_ge_relaxed(rk.peer_sync_flags[call.my_rank[lr]] + p, sm.epoch, call.timeout_ns)) {
                     atomicMax(&sm.timeout_peer, p);
                     report_error(rk.status, UEP_DEV_TIMEOUT_SYNC, p);
                 }
