@@ -146,11 +146,12 @@ class ForwardWorkload:
         # routing ids: a pool of microbatches, on the device and in pinned host memory. The
         # ranks hosted here share one contiguous buffer per direction, so a step's input is one
         # host->device copy and its result one device->host copy.
-        self.ids_host, self.ids_dev = [], []
+        self.ids_host, self.ids_dev, self.ids_all_dev = [], [], []
         for mb in range(num_microbatches):
             host = torch.from_numpy(np.stack([W.routing_ids(cfg, r, microbatch=mb) for r in ranks])).pin_memory()
             self.ids_host.append(host)
             dev_all = host.to(dev)
+            self.ids_all_dev.append(dev_all)
             self.ids_dev.append([dev_all[i] for i in range(len(ranks))])
         self.stage_all = torch.empty_like(self.ids_host[0], device=dev)
         self.ids_stage = [self.stage_all[i] for i in range(len(ranks))]
@@ -291,6 +292,28 @@ def run_ours(args):
     e2e_ms = sum(a.elapsed_time(b) for a, b in e2e_events) / len(e2e_events)
     group.check_status()
 
+    # ---- the same step captured once into a CUDA graph and replayed (device-resident inputs) ---
+    graph_ms = None
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            wl.step(0, wl.ids_stage)  # sizes are final: nothing allocates during the capture
+        torch.cuda.current_stream().wait_stream(side)
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            wl.step(0, wl.ids_stage)
+        barrier()
+        graph_events = []
+        for i in range(args.steps):
+            wl.stage_all.copy_(wl.ids_all_dev[i % len(wl.ids_all_dev)], non_blocking=True)
+            wl.flush_l2()
+            graph_events.append(event_ms(torch, graph.replay))
+        barrier()
+        graph_ms = sum(a.elapsed_time(b) for a, b in graph_events) / len(graph_events)
+        group.check_status()
+
     # ---- per-operation breakdown and the roofline of the weight_sync kernel -----------------
     comm = group.comm_stream()
     plan_ms, sync_ms, reroute_ms = [], [], []
@@ -342,6 +365,8 @@ def run_ours(args):
 
     mean_ms = max_over_ranks(mean_ms)
     e2e_ms = max_over_ranks(e2e_ms)
+    if graph_ms is not None:
+        graph_ms = max_over_ranks(graph_ms)
     sync_each_ms = max_over_ranks_each(sync_ms)  # per launch: the slowest rank
     sync_total_ms = sum(sync_each_ms)
     plan_mean = max_over_ranks(sum(plan_ms) / nb)
@@ -392,6 +417,10 @@ def run_ours(args):
                              "step_min": round(min(step_ms) * 1e3, 2), "step_max": round(max(step_ms) * 1e3, 2)},
             "wall_s_timed_region": round(t_wall, 3),
         }
+        if graph_ms is not None:
+            out["graph_replay"] = {"value": round(graph_ms * 1e3, 2), "unit": UNIT,
+                                   "note": "the same step (same three calls) captured once into a CUDA graph and replayed; "
+                                           "a step always works on layer slot 0 of the plan storage"}
         if cpu is not None:
             out["cpu_baseline"] = cpu
         if ref is not None:
@@ -743,6 +772,7 @@ def main():
     ap.add_argument("--cpu-budget-s", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph replay figure")
     ap.add_argument("--no-backward", action="store_true", help="skip the backward-path figures (cfg4)")
     ap.add_argument("--reduce-sms", type=int, default=42, help="CTAs of the Wgrad reduce kernel (reference default 42)")
     args = ap.parse_args()

@@ -210,7 +210,12 @@ typedef enum uep_buffer_id {
     UEP_BUF_REPLICA_FC2_SCALE,  /* uint8 [R, fc2_scaleB] strided */
     UEP_BUF_REPLICA_GRAD,       /* float [R, fc1+fc2]      */
     UEP_BUF_REPLICA_FC1_GRAD,   /* float [R, fc1] strided  */
-    UEP_BUF_REPLICA_FC2_GRAD    /* float [R, fc2] strided  */
+    UEP_BUF_REPLICA_FC2_GRAD,   /* float [R, fc2] strided  */
+    /* Tokens each physical slot receives under the stored plan (its quota; 0 for an empty slot),
+     * written by the plan kernel as it emits the plan. Replaces the reference's separate
+     * profiling kernel profile_physical_loads_from_quota_triton (ultra_ep/util.py:72-176) and
+     * its scatter_add fallback (ultra_ep/manager.py:332-357). */
+    UEP_BUF_PHYSICAL_LOADS      /* int32 [layers, P]       */
 } uep_buffer_id;
 int uep_manager_buffer(uep_manager* m, int local_rank, int buffer_id, void** ptr, int* ndim, int64_t shape[3],
                        int64_t stride[3]);

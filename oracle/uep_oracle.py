@@ -202,6 +202,17 @@ def dense_reroute_backward(grad_expanded: np.ndarray, routing_map: np.ndarray, e
     return out
 
 
+def physical_loads_from_plan(plan: Plan, P: int) -> np.ndarray:
+    """Tokens per physical slot under a plan: quota[l, j] scattered to l2p[l, j] (ultra_ep/manager.py:345-357
+    of the reference, the scatter_add form of its profiling kernel)."""
+    out = np.zeros(P, np.int32)
+    l2p = np.asarray(plan.l2p).reshape(-1)
+    quota = np.asarray(plan.quota).reshape(-1)
+    valid = l2p >= 0
+    np.add.at(out, l2p[valid], quota[valid])
+    return out
+
+
 def dispatch_positions(phys_ids: np.ndarray, P: int):
     a = np.ascontiguousarray(phys_ids, dtype=np.int32).reshape(-1)
     pos = np.empty(a.size, np.int32)

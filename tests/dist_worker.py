@@ -11,6 +11,8 @@ are random (not exactly summable), so the accumulation order is pinned too.
 """
 
 import os
+import shutil
+import tempfile
 import sys
 
 import numpy as np
@@ -48,6 +50,12 @@ def main():
     fc1, fc2 = 2 * hidden * ffn, hidden * ffn
     s1, s2 = fc1 // 128, fc2 // 128 + 3  # fc2 scale bytes not a multiple of 16
     layers = 3
+    # expert-load trace: switched on through the reference's environment variables, checked at the end
+    trace_dir = tempfile.mkdtemp(prefix="uep_trace_") if rank == 0 else ""
+    if rank == 0:
+        os.environ["ULTRA_EP_LOAD_PROFILING"] = "1"
+        os.environ["ULTRA_EP_LOAD_PROFILE_DIR"] = trace_dir
+    trace_expect = []  # (virtual layer, global logical loads, physical loads) in call order
     mgr = Manager(dist.group.WORLD, layers, M, R, fc1, fc2, is_train=True, explicitly_destroy=True, max_microbatches=2,
                   weight_data_dtype=torch.uint8, weight_scale_dtype=torch.uint8, expert_fc1_weight_scale_numel=s1,
                   expert_fc2_weight_scale_numel=s2)
@@ -95,6 +103,9 @@ def main():
         mgr.check_status()
         dist.barrier()
 
+        if rank == 0:
+            trace_expect.append((vid, mgr.runtime.get_global_logical_expert_loads_tensor().cpu().numpy().copy(),
+                                 mgr._profile_physical_loads_from_quota(vid).cpu().numpy().copy()))
         got = {"p2l": mgr.physical_to_logical_map[vid], "l2p": mgr.logical_to_physical_map[vid],
                "lcnts": mgr.logical_replica_counts[vid], "quota": mgr.logical_instance_quota[vid],
                "quota_prefix": mgr.logical_instance_quota_prefix[vid], "rank_quota_prefix": mgr.rank_quota_prefix[vid]}
@@ -192,6 +203,21 @@ def main():
         print(f"[dist_worker] EP{world}: all checks passed; forward step {t.item() * 1e3:.1f} us (max over ranks, small layer)",
               flush=True)
     mgr.destroy()
+    if rank == 0:  # the trace holds every update_placement of this run; the checked ones come first
+        import glob
+        import json
+
+        manifest = json.load(open(glob.glob(os.path.join(trace_dir, "*.manifest.json"))[0]))
+        assert manifest["schema"] == "ultra_ep_trace_v1" and manifest["dropped_records"] == 0, manifest
+        rows = []
+        for path in sorted(glob.glob(os.path.join(trace_dir, "*.npz"))):
+            z = np.load(path)
+            rows += list(zip(z["virtual_layers"], z["pre_logical_loads"], z["post_physical_loads"]))
+        assert len(rows) >= len(trace_expect) > 0
+        for (vid_got, pre, post), (vid, exp_pre, exp_post) in zip(rows, trace_expect):
+            assert int(vid_got) == vid and np.array_equal(pre, exp_pre) and np.array_equal(post, exp_post)
+            assert int(post.sum()) == int(pre.sum())
+        shutil.rmtree(trace_dir, ignore_errors=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -67,6 +67,11 @@ def test_update_placement_all_input_kinds(native_lib, cuda_device, name):
     for r in range(cfg.ep):
         assert np.array_equal(group.buffer(r, capi.BUF_GLOBAL_LOADS).cpu().numpy(), lpr.sum(0))
         assert np.array_equal(group.buffer(r, capi.BUF_LOADS_PER_RANK).cpu().numpy(), lpr)
+        # per-slot loads written by the plan kernel = the reference's profiling formula over the plan
+        expected = O.physical_loads_from_plan(plans[r], group.P)
+        assert int(expected.sum()) == int(lpr.sum())
+        for layer in range(3):
+            assert np.array_equal(group.buffer(r, capi.BUF_PHYSICAL_LOADS)[layer].cpu().numpy(), expected)
     group.destroy()
 
 

@@ -131,3 +131,55 @@ def test_two_rank_bootstrap_over_gloo(tmp_path, native_lib):
          "--master-port", "29631", str(script)], env=env, capture_output=True, text=True, timeout=240)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def test_expert_load_trace_files(tmp_path, monkeypatch):
+    """The load trace writes the reference's file layout: a manifest and .npz chunks with the
+    arrays its viewer reads; record_interval thins the records, flush_interval cuts chunks."""
+    import json
+
+    import numpy as np
+    import torch
+
+    from ultra_ep_b200 import profiling
+
+    monkeypatch.setenv("ULTRA_EP_LOAD_PROFILING", "1")
+    monkeypatch.setenv("ULTRA_EP_LOAD_PROFILE_DIR", str(tmp_path))
+    monkeypatch.setenv("ULTRA_EP_LOAD_PROFILE_FLUSH_INTERVAL", "4")
+    monkeypatch.setenv("ULTRA_EP_LOAD_PROFILE_RECORD_INTERVAL", "2")
+    cfg = profiling.load_profile_config()
+    assert cfg.enabled and cfg.flush_interval == 4 and cfg.record_interval == 2
+    L, P = 6, 8
+    meta = {"ep_group_id": "abc", "ep_rank": 0, "ep_size": 2}
+    prof = profiling.ExpertLoadProfiler(cfg, group_rank=0, global_rank=0, metadata=meta, num_logical=L, num_physical=P)
+    other = profiling.ExpertLoadProfiler(cfg, group_rank=1, global_rank=1, metadata=meta, num_logical=L, num_physical=P)
+    assert prof.enabled and not other.enabled
+    sent = []
+    for mb in range(12):  # two real layers, alternating; every second microbatch of each is kept
+        real = mb % 2
+        pre = torch.arange(L, dtype=torch.int32) + mb
+        post = torch.arange(P, dtype=torch.int32) * 2 + mb
+        prof.record(virtual_layer=real * 3 + 1, real_layer=real, pre_logical_loads=pre, post_physical_loads=post)
+        other.record(real * 3 + 1, real, pre, post)
+        if (mb // 2) % 2 == 0:
+            sent.append((real, real * 3 + 1, mb // 2, pre.numpy(), post.numpy()))
+    prof.close()
+    prof.close()  # idempotent
+    manifest = json.loads(next(tmp_path.glob("*.manifest.json")).read_text())
+    assert manifest["schema"] == "ultra_ep_trace_v1" and manifest["chunks"] == 2 and manifest["dropped_records"] == 0
+    chunks = sorted(tmp_path.glob("*.chunk*.npz"))
+    assert len(chunks) == 2 and not list(tmp_path.glob("*.tmp"))
+    rows = []
+    for path in chunks:
+        z = np.load(path)
+        assert set(z.files) == {"metadata", "layers", "virtual_layers", "microbatches", "pre_logical_loads",
+                                "post_physical_loads"}
+        assert json.loads(str(z["metadata"]))["trace_id"] == manifest["trace_id"]
+        assert z["pre_logical_loads"].dtype == np.int32 and z["pre_logical_loads"].shape[1] == L
+        assert z["post_physical_loads"].shape[1] == P
+        for i in range(len(z["layers"])):
+            rows.append((int(z["layers"][i]), int(z["virtual_layers"][i]), int(z["microbatches"][i]),
+                         z["pre_logical_loads"][i], z["post_physical_loads"][i]))
+    assert len(rows) == len(sent) == 6
+    for got, exp in zip(rows, sent):
+        assert got[:3] == exp[:3] and np.array_equal(got[3], exp[3]) and np.array_equal(got[4], exp[4])

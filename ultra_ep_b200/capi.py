@@ -18,7 +18,8 @@ IPC_HANDLE_BYTES = 64
 # uep_buffer_id
 (BUF_P2L, BUF_L2P, BUF_LCNTS, BUF_QUOTA, BUF_QUOTA_PREFIX, BUF_RANK_QUOTA_PREFIX, BUF_GLOBAL_LOADS,
  BUF_LOADS_PER_RANK, BUF_REPLICA_WEIGHT, BUF_REPLICA_FC1_WEIGHT, BUF_REPLICA_FC2_WEIGHT, BUF_REPLICA_SCALE,
- BUF_REPLICA_FC1_SCALE, BUF_REPLICA_FC2_SCALE, BUF_REPLICA_GRAD, BUF_REPLICA_FC1_GRAD, BUF_REPLICA_FC2_GRAD) = range(17)
+ BUF_REPLICA_FC1_SCALE, BUF_REPLICA_FC2_SCALE, BUF_REPLICA_GRAD, BUF_REPLICA_FC1_GRAD, BUF_REPLICA_FC2_GRAD,
+ BUF_PHYSICAL_LOADS) = range(18)
 
 DEV_STATUS_NAMES = {
     0: "ok", 1: "timeout waiting for a peer's load row", 2: "timeout waiting for a peer's weight_sync flag",

@@ -39,6 +39,7 @@ struct RankDev {
 
 struct PlanPtrs {
     int32_t *p2l, *l2p, *lcnts, *quota, *quota_prefix, *rank_quota_prefix;
+    int32_t* physical_loads;  // [P] tokens per physical slot under this plan (may be null)
 };
 
 struct ShardLayout {  // bytes of the four weight shards and their place inside a replica slot

@@ -38,6 +38,7 @@ struct RankHost {
     bool peer_opened[kMaxPeers] = {false};      // mapped through cudaIpcOpenMemHandle
     int32_t* plan_blob = nullptr;               // [layers][stride]
     int32_t* rank_quota_prefix = nullptr;       // [layers][L][D]
+    int32_t* physical_loads = nullptr;          // [layers][P]
     int32_t* local_hist = nullptr;              // [Lpad]
     int* tickets = nullptr;                     // [4]: plan ticket, sync ticket, sync tile counter, spare
     uint64_t* epochs = nullptr;                 // [2]: plan epoch, sync epoch (device-counted)
@@ -89,6 +90,7 @@ PlanPtrs plan_ptrs(const uep_manager* m, const RankHost& r, int layer) {
     p.quota = p.lcnts + m->L;
     p.quota_prefix = p.quota + static_cast<int64_t>(m->L) * m->D;
     p.rank_quota_prefix = r.rank_quota_prefix + static_cast<int64_t>(layer) * m->L * m->D;
+    p.physical_loads = r.physical_loads + static_cast<int64_t>(layer) * m->P;
     return p;
 }
 
@@ -164,6 +166,7 @@ void free_rank(RankHost& r, int my_rank_count) {
     cudaFree(r.arena);
     cudaFree(r.plan_blob);
     cudaFree(r.rank_quota_prefix);
+    cudaFree(r.physical_loads);
     cudaFree(r.local_hist);
     cudaFree(r.tickets);
     cudaFree(r.epochs);
@@ -310,6 +313,8 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
         UEP_TRY_BAIL(cudaMalloc(&r.plan_blob, sizeof(int32_t) * m->layer_stride * cfg->num_layers));
         UEP_TRY_BAIL(cudaMemset(r.plan_blob, 0, sizeof(int32_t) * m->layer_stride * cfg->num_layers));
         UEP_TRY_BAIL(cudaMalloc(&r.rank_quota_prefix, sizeof(int32_t) * static_cast<size_t>(m->L) * m->D * cfg->num_layers));
+        UEP_TRY_BAIL(cudaMalloc(&r.physical_loads, sizeof(int32_t) * static_cast<size_t>(m->P) * cfg->num_layers));
+        UEP_TRY_BAIL(cudaMemset(r.physical_loads, 0, sizeof(int32_t) * static_cast<size_t>(m->P) * cfg->num_layers));
         UEP_TRY_BAIL(cudaMalloc(&r.local_hist, sizeof(int32_t) * m->Lpad));
         UEP_TRY_BAIL(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
         UEP_TRY_BAIL(cudaMalloc(&r.tickets, sizeof(int) * 4));
@@ -428,6 +433,7 @@ int uep_manager_buffer(uep_manager* m, int local_rank, int buffer_id, void** ptr
         case UEP_BUF_QUOTA: set(blob + P + L * D + L, 3, layers, L, D, m->layer_stride, D, 1); break;
         case UEP_BUF_QUOTA_PREFIX: set(blob + P + 2 * L * D + L, 3, layers, L, D, m->layer_stride, D, 1); break;
         case UEP_BUF_RANK_QUOTA_PREFIX: set(r.rank_quota_prefix, 3, layers, L, D, L * D, D, 1); break;
+        case UEP_BUF_PHYSICAL_LOADS: set(r.physical_loads, 2, layers, P, 1, P, 1, 1); break;
         case UEP_BUF_GLOBAL_LOADS: set(r.global_loads, 1, L, 1, 1, 1, 1, 1); break;
         case UEP_BUF_LOADS_PER_RANK: set(r.loads_per_rank, 2, m->N, L, 1, L, 1, 1); break;
         case UEP_BUF_REPLICA_WEIGHT: set(w, 2, R, m->weight_stride, 1, m->weight_stride, 1, 1); break;

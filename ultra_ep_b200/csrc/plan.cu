@@ -256,6 +256,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     const PlanPtrs& pp = call.plan[local];
     a.p2l = pp.p2l; a.l2p = pp.l2p; a.lcnts = pp.lcnts; a.quota = pp.quota; a.quota_prefix = pp.quota_prefix;
     a.rank_quota_prefix = pp.rank_quota_prefix;
+    a.physical_loads = pp.physical_loads;
     a.N = N; a.G = call.G; a.M = M; a.R = call.R; a.D = call.D;
     a.balance_threshold = call.params.balance_threshold;
     a.min_tokens = call.params.min_tokens_per_replica;
@@ -370,6 +371,7 @@ int uep_solve_placement(const int32_t* loads_per_rank, int32_t* global_loads_out
     a.loads_per_rank = loads_per_rank;
     a.p2l = p2l; a.l2p = l2p; a.lcnts = lcnts; a.quota = quota; a.quota_prefix = quota_prefix;
     a.rank_quota_prefix = rank_quota_prefix;
+    a.physical_loads = nullptr;
     a.N = num_ranks; a.G = nvl_ranks; a.M = M; a.R = R; a.D = D;
     a.balance_threshold = params->balance_threshold;
     a.min_tokens = params->min_tokens_per_replica;

@@ -35,6 +35,7 @@ struct SolveArgs {
     int32_t* quota;                 // [L, D]
     int32_t* quota_prefix;          // [L, D]
     int32_t* rank_quota_prefix;     // [L, D]
+    int32_t* physical_loads;        // [P] quota of every physical slot, 0 when empty (optional: may be null)
     int N, G, M, R, D;
     float balance_threshold;
     int min_tokens;
@@ -408,7 +409,10 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
     stamp(0);
 
     // Clear this domain's slice of every output, then place the masters.
-    for (int i = tid; i < G * Lp; i += nthreads) a.p2l[domain_start_rank * Lp + i] = -1;
+    for (int i = tid; i < G * Lp; i += nthreads) {
+        a.p2l[domain_start_rank * Lp + i] = -1;
+        if (a.physical_loads != nullptr) a.physical_loads[domain_start_rank * Lp + i] = 0;
+    }
     for (int i = tid; i < E * D; i += nthreads) {
         const int64_t idx = static_cast<int64_t>(domain_start_log) * D + i;
         a.l2p[idx] = -1;
@@ -616,7 +620,9 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
     int* multi_list = sm.export_sum + E;
     for (int e = tid; e < E; e += nthreads) {
         const int64_t row = static_cast<int64_t>(domain_start_log + e) * D;
-        a.quota[row] = do_search ? (sm.loads[e] - sm.export_sum[e]) : sm.loads[e];
+        const int master_quota = do_search ? (sm.loads[e] - sm.export_sum[e]) : sm.loads[e];
+        a.quota[row] = master_quota;
+        if (a.physical_loads != nullptr) a.physical_loads[(domain_start_rank + e / M) * Lp + e % M] = master_quota;
     }
     if (tid == 0) sm.ctrl[kCtlMultiCount] = 0;
     __syncthreads();
@@ -649,6 +655,7 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
                     a.p2l[phys] = l_global;
                     a.l2p[row + slot] = phys;
                     a.quota[row + slot] = entry.quota;
+                    if (a.physical_loads != nullptr) a.physical_loads[phys] = entry.quota;
                     sm.plan[k].target_rank_local = phys;  // from here on the entry carries the physical id
                 }
             }

@@ -510,7 +510,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("get_logical_instance_quota_prefix_tensor", [](const Manager& s) { return s.buf(UEP_BUF_QUOTA_PREFIX, torch::kInt32); })
         .def("get_rank_quota_prefix_tensor", [](const Manager& s) { return s.buf(UEP_BUF_RANK_QUOTA_PREFIX, torch::kInt32); })
         .def("get_global_logical_expert_loads_tensor", [](const Manager& s) { return s.buf(UEP_BUF_GLOBAL_LOADS, torch::kInt32); })
-        .def("get_expert_loads_per_rank_tensor", [](const Manager& s) { return s.buf(UEP_BUF_LOADS_PER_RANK, torch::kInt32); });
+        .def("get_expert_loads_per_rank_tensor", [](const Manager& s) { return s.buf(UEP_BUF_LOADS_PER_RANK, torch::kInt32); })
+        .def("get_physical_expert_loads_tensor", [](const Manager& s) { return s.buf(UEP_BUF_PHYSICAL_LOADS, torch::kInt32); });
 
     m.def("solve_placement_for_test", &solve_placement_for_test, py::arg("expert_loads"), py::arg("expert_loads_per_rank"),
           py::arg("num_ranks"), py::arg("num_local_master_experts"), py::arg("num_local_redundant_experts"),

@@ -2,8 +2,9 @@
 
 Drop-in for the reference's ultra_ep.Manager (ultra_ep/manager.py:18-770 of the reference): same
 constructor arguments, methods, properties, buffer attributes and virtual-layer arithmetic.
-Differences: the expert-load profiler and its viewer are not part of this library (the
-ULTRA_EP_LOAD_PROFILING switches are ignored), and legacy_placement=True is refused.
+Differences: the expert-load trace (ULTRA_EP_LOAD_PROFILING) is recorded when the plan is made,
+from the per-slot loads the plan kernel writes itself, instead of by a separate kernel at reroute
+time (same trace files); its viewer is not part of this library; legacy_placement=True is refused.
 """
 
 from __future__ import annotations
@@ -16,6 +17,7 @@ import torch.distributed as dist
 from .config import load_tuning_from_env
 from .event import EventHandle
 from .native import load
+from .profiling import ExpertLoadProfiler, load_profile_config
 from .reroute import _DenseRerouteFunction
 from .runtime import init_runtime
 from .util import check_dtype, dtype_element_size
@@ -154,6 +156,22 @@ class Manager:
             self.local_replica_fc1_grad_buffer = None
             self.local_replica_fc2_grad_buffer = None
         self.check_tensors_blob_from_cpp()
+        self._physical_expert_loads = rt.get_physical_expert_loads_tensor()
+        self._load_profiler = ExpertLoadProfiler(
+            config=load_profile_config(),
+            group_rank=self.rank,
+            global_rank=dist.get_rank() if dist.is_initialized() else self.rank,
+            metadata={
+                "ep_group_id": f"{self.id:x}", "ep_rank": self.rank, "ep_size": self.num_ranks,
+                "num_layers": self.num_layers, "max_microbatches": self.max_microbatches,
+                "num_local_master_experts": self.num_local_master_experts,
+                "num_local_redundant_experts": self.num_local_redundant_experts,
+                "num_local_physical_experts": self.num_local_physical_experts,
+                "num_global_logical_experts": self.num_global_logical_experts,
+                "num_global_physical_experts": self.num_global_physical_experts,
+                "nvl_domain_size": self.nvl_domain_size, "placement_mode": self.reroute_mode,
+            },
+            num_logical=self.num_global_logical_experts, num_physical=self.num_global_physical_experts)
 
     # -- plan maps (device resident, all virtual layers) -----------------------------------
     @property
@@ -194,6 +212,7 @@ class Manager:
         if self.runtime is not None:
             torch.cuda.synchronize()
             dist.barrier(group=self.group)  # no peer may still be writing into this rank's slots
+            self._load_profiler.close()
             self.runtime.destroy()
         self.runtime = None
 
@@ -293,6 +312,7 @@ class Manager:
         assert layer_id < self.num_alloc_layers
         with torch.cuda.nvtx.range(f"Update placement (layer {layer_id})"):
             self.runtime.update_placement(layer_id, routing_map)
+        self._record_loads(layer_id)
         if verify_reduced_loads:
             loads = routing_map.sum(dim=0, dtype=torch.int32)
             dist.all_reduce(loads, group=self.group)
@@ -302,6 +322,21 @@ class Manager:
         """Same from top-k ids [tokens, k] (int64, or int32); runs on the communication stream."""
         assert layer_id < self.num_alloc_layers
         self.runtime.update_placement_sparse(layer_id, topk_ids)
+        if self._load_profiler.enabled:
+            with torch.cuda.stream(self.get_comm_stream()):
+                self._record_loads(layer_id)
+
+    def _record_loads(self, layer_id: int):
+        """Expert-load trace: loads before balancing (logical) and after it (physical slots)."""
+        if self._load_profiler.enabled:
+            self._load_profiler.record(layer_id, self._real_layer_id(layer_id),
+                                       self.runtime.get_global_logical_expert_loads_tensor(),
+                                       self._physical_expert_loads[layer_id])
+
+    def _profile_physical_loads_from_quota(self, layer_id: int, fused: bool = True) -> torch.Tensor:
+        """Tokens per physical slot under the layer's plan: int32 [physical experts]. The plan kernel
+        writes this vector itself; `fused` is accepted for compatibility and has no effect."""
+        return self._physical_expert_loads[layer_id]
 
     def reroute(self, layer_id: int, probs: torch.Tensor, routing_map: torch.Tensor, backend: str = "cuda"):
         """Expand [tokens, logical] probabilities and routing map to [tokens, physical] under this

@@ -46,6 +46,7 @@ _BUF_DTYPE = {
     capi.BUF_REPLICA_FC2_WEIGHT: torch.uint8, capi.BUF_REPLICA_SCALE: torch.uint8, capi.BUF_REPLICA_FC1_SCALE: torch.uint8,
     capi.BUF_REPLICA_FC2_SCALE: torch.uint8, capi.BUF_REPLICA_GRAD: torch.float32,
     capi.BUF_REPLICA_FC1_GRAD: torch.float32, capi.BUF_REPLICA_FC2_GRAD: torch.float32,
+    capi.BUF_PHYSICAL_LOADS: torch.int32,
 }
 
 
