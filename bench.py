@@ -185,23 +185,31 @@ class ForwardWorkload:
         self.stage_all.copy_(self.ids_host[i % len(self.ids_host)], non_blocking=True)
         self.step(i, self.ids_stage, result_to_host=True)
 
-    def sync_bytes(self, layer):
+    def sync_bytes(self, layer, relay_min=0):
         """Algorithmic bytes of one weight_sync launch of the hosted ranks: every replicated
-        master is read once and written once per replica."""
+        master is read once and written once per replica. egress / ingress: the largest per-rank
+        NVLink volume in each direction; with relaying (experts with >= relay_min replicas) a master's
+        rank sends such an expert once and each of its r replicas forwards (r-1)/r of it."""
         cfg = self.cfg
         total_read = total_write = 0
         egress = ingress = 0
+        Lp = cfg.masters + cfg.redundant
         for li, r in enumerate(self.ranks):
             lc = self.group.buffer(li, 2)[layer].cpu().numpy()  # BUF_LCNTS
             p2l = self.group.buffer(li, 0)[layer].cpu().numpy()  # BUF_P2L
-            mine = lc[r * cfg.masters:(r + 1) * cfg.masters]
-            reps = int((mine - 1).clip(min=0).sum())
-            total_read += int((mine > 1).sum()) * cfg.expert_bytes
-            total_write += reps * cfg.expert_bytes
-            egress = max(egress, reps * cfg.expert_bytes)
-            Lp = cfg.masters + cfg.redundant
-            used = int((p2l.reshape(cfg.ep, Lp)[r, cfg.masters:] >= 0).sum())
-            ingress = max(ingress, used * cfg.expert_bytes)
+            reps_of = (lc - 1).clip(min=0)
+            relayed = (reps_of >= max(relay_min, 2)) if relay_min > 0 else np.zeros_like(reps_of, bool)
+            mine = np.arange(r * cfg.masters, (r + 1) * cfg.masters)
+            total_read += int((reps_of[mine] > 0).sum()) * cfg.expert_bytes
+            total_write += int(reps_of[mine].sum()) * cfg.expert_bytes
+            out = float(np.where(relayed[mine], np.minimum(reps_of[mine], 1), reps_of[mine]).sum())
+            hosted = p2l.reshape(cfg.ep, Lp)[r, cfg.masters:]
+            hosted = hosted[hosted >= 0]
+            out += float(sum((reps_of[l] - 1) / reps_of[l] for l in hosted if relayed[l]))
+            if relay_min > 0:  # a forwarded tile is read again from the slot it landed in (its writes are counted above)
+                total_read += int(sum(cfg.expert_bytes * (reps_of[l] - 1) / reps_of[l] for l in hosted if relayed[l]))
+            egress = max(egress, out * cfg.expert_bytes)
+            ingress = max(ingress, len(hosted) * cfg.expert_bytes)
         return total_read, total_write, egress, ingress
 
 
@@ -236,7 +244,8 @@ def run_ours(args):
         mcfg = sim.make_config(world, cfg.masters, cfg.redundant, num_layers, fc1_numel=cfg.fc1_numel,
                                fc2_numel=cfg.fc2_numel, weight_elem_bytes=cfg.weight_elem_bytes,
                                fc1_scale_numel=cfg.fc1_scale_numel, fc2_scale_numel=cfg.fc2_scale_numel, is_train=False,
-                               rank=rank, sim=False, weight_sync_num_sms=args.sync_sms)
+                               rank=rank, sim=False, weight_sync_num_sms=args.sync_sms, plan_mode=args.plan_mode,
+                               relay_min_replicas=args.relay_min_replicas)
         group = sim.IpcGroup(mcfg, dist.group.WORLD)
         ranks = [rank]
     else:
@@ -244,7 +253,8 @@ def run_ours(args):
         mcfg = sim.make_config(cfg.ep, cfg.masters, cfg.redundant, num_layers, fc1_numel=cfg.fc1_numel,
                                fc2_numel=cfg.fc2_numel, weight_elem_bytes=cfg.weight_elem_bytes,
                                fc1_scale_numel=cfg.fc1_scale_numel, fc2_scale_numel=cfg.fc2_scale_numel, is_train=False,
-                               sim=True, weight_sync_num_sms=args.sync_sms)
+                               sim=True, weight_sync_num_sms=args.sync_sms, plan_mode=args.plan_mode,
+                               relay_min_replicas=args.relay_min_replicas)
         group = sim.SimGroup(mcfg)
         ranks = list(range(cfg.ep))
     wl = ForwardWorkload(cfg, group, ranks, num_microbatches=8, num_layers=num_layers)
@@ -339,7 +349,8 @@ def run_ours(args):
                             stream=comm)
         barrier()
         sync_ms.append(a.elapsed_time(b))
-        r_, w_, eg, ig = wl.sync_bytes(layer)
+        relay_min = 0 if args.plan_mode == 0 else (2 if args.plan_mode == 2 else max(2, args.relay_min_replicas))
+        r_, w_, eg, ig = wl.sync_bytes(layer, relay_min)
         rd, wr = rd + r_, wr + w_
         link_bytes.append(float(max(eg, ig)))
         wl.flush_l2()
@@ -405,6 +416,7 @@ def run_ours(args):
                             + ("EP8 simulated on one GPU (8 ranks per launch)" if world == 1 else f"EP{world}, one rank per GPU"),
                 "experts": cfg.num_experts, "topk": cfg.topk, "tokens_per_rank": cfg.tokens_per_rank,
                 "redundant_per_rank": cfg.redundant, "expert_bytes": cfg.expert_bytes, "zipf_s": cfg.zipf_s,
+                "weight_sync_plan_mode": args.plan_mode,
                 "l2": "between timed steps a 256 MiB buffer is written, then a second 256 MiB buffer is read", "microbatch_pool": 8,
             },
             "clocks": clocks,
@@ -769,6 +781,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg3_qwen3_235b_fp8")
     ap.add_argument("--sync-sms", type=int, default=0, help="CTAs per rank of the weight_sync kernel (0 = default)")
+    ap.add_argument("--plan-mode", type=int, default=0, choices=[0, 1, 2],
+                    help="weight_sync: 0 direct fan-out, 1 relay experts with >= --relay-min-replicas replicas, 2 relay all with >= 2")
+    ap.add_argument("--relay-min-replicas", type=int, default=4)
     ap.add_argument("--cpu-budget-s", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref", action="store_true")

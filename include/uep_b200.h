@@ -170,7 +170,8 @@ typedef struct uep_config {
     int32_t quota_kernel_stage;         /* 0 or 1; both give identical plans, accepted for compatibility */
     int32_t grad_reduce_num_sms;        /* even, > 0, clamped to the SM count                */
     int32_t grad_reduce_deterministic;  /* 0 accepted; the fixed-order kernel always runs    */
-    int32_t weight_sync_plan_mode;      /* 0 direct, 1 adaptive, 2 force relay; only direct fan-out is executed */
+    int32_t weight_sync_plan_mode;      /* 0 direct; 1 adaptive: experts with >= relay_min_replicas replicas are relayed
+                                         * (scatter over the replicas + replica-to-replica forward); 2 force relay (>= 2) */
     int32_t weight_sync_relay_min_replicas, weight_sync_relay_max_relays, weight_sync_relay_min_fanout_gain;
     int32_t weight_sync_num_sms;        /* CTAs of the copy kernel per rank; 0 = default     */
     int32_t wait_timeout_ms;            /* bound of every device-side wait; 0 = default 5000 */

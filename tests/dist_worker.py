@@ -72,7 +72,9 @@ def main():
     for real_layer in range(1, layers + 1):
         mgr.construct_local_master_ptr_pool(real_layer, mine[0], mine[1], fc1_g, fc2_g, mine[2], mine[3])
 
-    for it in range(5):
+    for it in range(6):
+        if it == 3:  # the second half runs with every multi-replica expert relayed (scatter + forward)
+            mgr.set_weight_sync_plan_mode("force_relay")
         real_layer = 1 + it % layers
         vid = mgr.allocate_microbatch_slot(real_layer)
         ids_all = [W.routing_ids(cfg, r, microbatch=it) for r in range(N)]

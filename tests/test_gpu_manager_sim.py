@@ -148,24 +148,27 @@ def _master_tensors(cfg, group, nbytes_per_shard, misalign=0):
     (2 * 96 * 128, 96 * 128, 100, 50, 1, 8),        # masters not 16-byte aligned: plain copy path
     (33 * 1024 * 16, 16, 0, 0, 1, 0),               # several tiles per shard and a one-vector shard
 ])
-def test_weight_sync_bitwise(native_lib, cuda_device, fc1, fc2, s1, s2, elem, misalign):
-    cfg = W.CONFIGS["cfg1_plan_reroute"]
-    group = make_group(cfg, fc1=fc1, fc2=fc2, elem=elem, s1=s1, s2=s2)
-    ids = [torch.from_numpy(W.routing_ids(cfg, r)).to(cuda_device) for r in range(cfg.ep)]
+@pytest.mark.parametrize("plan_mode", [0, 2, 1])  # direct; every expert with >= 2 replicas relayed; adaptive (>= 3 here)
+def test_weight_sync_bitwise(native_lib, cuda_device, fc1, fc2, s1, s2, elem, misalign, plan_mode):
+    # cfg 3's routing of microbatch 1 gives experts with one, two and three replicas
+    cfg = small_cfg("cfg3_qwen3_235b_fp8")
+    group = make_group(cfg, fc1=fc1, fc2=fc2, elem=elem, s1=s1, s2=s2, relay_min_replicas=3)
+    capi.check(group.lib.uep_set_weight_sync_plan_mode(group.handle, plan_mode))
+    ids = [torch.from_numpy(W.routing_ids(cfg, r, microbatch=1)).to(cuda_device) for r in range(cfg.ep)]
     group.update_placement(0, ids)
     nbytes = [fc1 * elem, fc2 * elem] + ([s1, s2] if s1 + s2 else [])
     shards = _master_tensors(cfg, group, nbytes, misalign)
     tables = [group.pointer_tables(sh) for sh in shards] + [None] * (4 - len(shards))
-    w_before, s_before = [], []
-    for r in range(cfg.ep):
-        w = group.buffer(r, capi.BUF_REPLICA_WEIGHT)
-        w.random_(0, 256)
-        w_before.append(w.clone())
-        sbuf = group.buffer(r, capi.BUF_REPLICA_SCALE)
-        if sbuf.numel():
-            sbuf.random_(0, 256)
-        s_before.append(sbuf.clone())
-    for rep in range(2):  # twice: epochs advance, result identical
+    for rep in range(3):  # several epochs; the slots are re-randomised so that every epoch has to deliver
+        w_before, s_before = [], []
+        for r in range(cfg.ep):
+            w = group.buffer(r, capi.BUF_REPLICA_WEIGHT)
+            w.random_(0, 256)
+            w_before.append(w.clone())
+            sbuf = group.buffer(r, capi.BUF_REPLICA_SCALE)
+            if sbuf.numel():
+                sbuf.random_(0, 256)
+            s_before.append(sbuf.clone())
         ev = group.weight_sync(0, *tables, async_finish=bool(rep))
         if ev is not None:
             group.wait_event(ev)
@@ -173,6 +176,8 @@ def test_weight_sync_bitwise(native_lib, cuda_device, fc1, fc2, s1, s2, elem, mi
         group.check_status()
     plan = O.Plan(**{f: group.plan(0, 0)[f].cpu().numpy() for f in PLAN_FIELDS})
     assert int((plan.lcnts > 1).sum()) > 0, "the case must replicate something"
+    if plan_mode:
+        assert int((plan.lcnts > 3).sum()) > 0 and int((plan.lcnts == 3).sum()) > 0 and int((plan.lcnts == 2).sum()) > 0
     for r in range(cfg.ep):
         exp_w = w_before[r].cpu().numpy()
         offs = [0, fc1 * elem]

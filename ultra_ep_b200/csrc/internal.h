@@ -31,6 +31,7 @@ struct RankDev {
     uint8_t* peer_replica_scale[kMaxPeers];
     float* peer_replica_grad[kMaxPeers];
     uint64_t* peer_sync_flags[kMaxPeers];  // each: [N], entry [src] = last epoch src finished sending to that rank
+    uint64_t* peer_relay_flags[kMaxPeers]; // each: [R][relay_cap], entry [slot][tile] = epoch in which the master delivered that tile
     DeviceStatus* status;    // mapped pinned host memory
     // [0] plan epoch, [1] sync epoch: counted on the device (by the CTA that finishes a launch), not
     // passed by value, so that a captured CUDA graph can be replayed: every replay is a new epoch
@@ -81,6 +82,10 @@ struct SyncCall {
     uint64_t timeout_ns;
     int ctas_per_rank;
     int withhold_rank;  // test hook, as in PlanCall
+    int relay_min_replicas;  // 0: every master writes all its replicas itself; else experts with at least this many
+                             // replicas are scattered over them and forwarded replica to replica
+    int relay_cap;           // tiles per slot the ready-flag table has room for
+    uint64_t* sync_epoch;    // the sync epoch counter of the first hosted rank (by value: one load, not two)
     unsigned long long* trace;  // optional: 8 globaltimer stamps per CTA (tuning aid), or null
 };
 cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream);

@@ -28,7 +28,7 @@ struct uep_event {
 namespace {
 
 struct ArenaLayout {
-    size_t gather, sync_flags, replica_weight, replica_scale, replica_grad, total;
+    size_t gather, sync_flags, relay_flags, replica_weight, replica_scale, replica_grad, total;
 };
 
 struct RankHost {
@@ -74,6 +74,7 @@ struct uep_manager {
     int grad_reduce_ctas = 42;
     int weight_sync_ctas = 0;
     int withhold_rank = -1;
+    int relay_cap = 0;  // ready-flag words per replica slot
     unsigned long long* sync_trace = nullptr;  // UEP_SYNC_TRACE=1: per-CTA phase stamps of the last weight_sync
 };
 
@@ -148,6 +149,7 @@ int upload_rank_dev(uep_manager* m, RankHost& r) {
         if (base == nullptr) return fail(UEP_ERR_STATE, "connect: a peer arena is not mapped");
         d.peer_gather[p] = reinterpret_cast<uint64_t*>(base + m->arena.gather);
         d.peer_sync_flags[p] = reinterpret_cast<uint64_t*>(base + m->arena.sync_flags);
+        d.peer_relay_flags[p] = reinterpret_cast<uint64_t*>(base + m->arena.relay_flags);
         d.peer_replica_weight[p] = base + m->arena.replica_weight;
         d.peer_replica_scale[p] = base + m->arena.replica_scale;
         d.peer_replica_grad[p] = reinterpret_cast<float*>(base + m->arena.replica_grad);
@@ -288,6 +290,10 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
     size_t off = 0;
     m->arena.gather = off;        off = align256(off + sizeof(uint64_t) * 2 * N * m->Lpad);
     m->arena.sync_flags = off;    off = align256(off + sizeof(uint64_t) * N);
+    // ready flags of relayed tiles: one word per (replica slot, tile), sized for the smallest tile geometry
+    m->relay_cap = 4;
+    for (int64_t b : {m->fc1_bytes, m->fc2_bytes, m->fc1_scale_bytes, m->fc2_scale_bytes}) m->relay_cap += static_cast<int>((b + 8191) / 8192);
+    m->arena.relay_flags = off;   off = align256(off + sizeof(uint64_t) * static_cast<size_t>(R) * m->relay_cap);
     m->arena.replica_weight = off; off = align256(off + static_cast<size_t>(R) * m->weight_stride);
     m->arena.replica_scale = off;  off = align256(off + static_cast<size_t>(R) * m->scale_stride);
     m->arena.replica_grad = off;
@@ -535,6 +541,12 @@ int uep_weight_sync(uep_manager* m, int layer_id, const int64_t* const* fc1_ptrs
     call.timeout_ns = m->timeout_ns;
     call.ctas_per_rank = m->weight_sync_ctas;
     call.withhold_rank = m->withhold_rank;
+    // plan mode 0: every master writes all its replicas; 1: experts with at least relay_min_replicas replicas are
+    // scattered over their replicas and forwarded replica to replica; 2: every expert with two or more replicas is
+    const int mode = m->cfg.weight_sync_plan_mode;
+    call.relay_min_replicas = mode == 0 ? 0 : (mode == 2 ? 2 : std::max(2, m->cfg.weight_sync_relay_min_replicas));
+    call.relay_cap = m->relay_cap;
+    call.sync_epoch = m->ranks[0].epochs + 1;
     call.trace = m->sync_trace;
     if (m->R > 0) UEP_CUDA_TRY(launch_weight_sync(call, m->comm_stream));
     return finish_sync_op(m, async_finish, current, done_event);
@@ -646,7 +658,7 @@ int uep_set_weight_sync_plan_mode(uep_manager* m, int plan_mode) {
     if (m == nullptr) return fail(UEP_ERR_INVALID, "set_weight_sync_plan_mode: null manager");
     if (plan_mode < 0 || plan_mode > 2) return fail(UEP_ERR_INVALID, "set_weight_sync_plan_mode: plan_mode must be 0, 1 or 2");
     UEP_CUDA_TRY(cudaDeviceSynchronize());  // as the reference does (csrc/ultra_ep.cpp:989)
-    m->cfg.weight_sync_plan_mode = plan_mode;  // recorded; only the direct fan-out is executed
+    m->cfg.weight_sync_plan_mode = plan_mode;
     return UEP_OK;
 }
 

@@ -6,7 +6,7 @@
 // 8 ranks, or a two-stage bulk-copy kernel above that (csrc/kernels/weight_sync.cu:205-522,
 // 714-775, 782-986 of the reference). Here there is no task list and one kernel:
 //   * every CTA derives the send list from the plan rows of this rank's masters
-//     (l2p / lcnts) with a block-wide scan, a few hundred nanoseconds of work;
+//     (l2p / lcnts) with a block-wide scan; all global reads of the set-up are issued together;
 //   * one elected thread per CTA drives a 4-stage ring of 32 KiB bulk copies: the tile is
 //     read from local HBM once (cp.async.bulk global->shared, mbarrier) and stored to each
 //     destination slot (cp.async.bulk shared->global, peer memory over NVLink); loads run
@@ -16,8 +16,17 @@
 //   * the CTA that finishes last publishes "rank r has delivered epoch e" to the ranks it
 //     sent to (system-scope release) and waits, bounded, for the same word from the ranks
 //     that send to it. When the kernel ends, this rank's replica slots are complete.
-//     No CTA waits for another CTA of the same launch.
 // Pointers or sizes that are not multiples of 16 bytes take a plain vector/byte copy path.
+//
+// Relay (optional; the reference's relay plan, csrc/kernels/weight_sync.cu:129-191, 295-502,
+// exists only for NVLink domains above 8 ranks). An expert with r >= relay_min_replicas replicas
+// is broadcast as scatter + forward: its master sends tile t only to replica t mod r and raises
+// that tile's ready flag there; every replica forwards the tiles it received from the master to
+// the other r-1 replicas. The master's rank then sends the expert once instead of r times, and
+// the forwarding load is spread over the replicas' ranks. Whether an expert is relayed is a pure
+// function of the plan, so all ranks agree without talking. Forward tiles sit behind all send
+// tiles in the hand-out order: a CTA that waits (bounded) for a ready flag waits for a tile that
+// a running CTA, on this or another device, is already sending.
 
 #include <cstdio>
 #include <cstdlib>
@@ -29,44 +38,61 @@ namespace uep {
 namespace {
 
 constexpr int kSyncThreads = 128;
-constexpr int kSyncTileDefault = 32 * 1024;
-constexpr int kSyncStagesDefault = 4;
 constexpr int kMaxSends = kMaxExportsPerDomain;  // replicas of one rank's masters never exceed G*R <= 512
+constexpr int kMaxFwd = 64;                       // replica slots of the hosted ranks that may forward
+constexpr int kMaxRelayReplicas = 16;
+constexpr int kMaxFwdDst = kMaxFwd * (kMaxRelayReplicas - 1);
 
 struct SyncShared {
     int n_active;          // masters (of all hosted ranks) that have replicas
     int total_reps;        // sum of their replica counts
     int all_aligned;       // every source pointer 16-byte aligned
     int is_last;
-    unsigned send_mask[kMaxLocalRanks][3];  // per hosted rank: ranks it sends to
-    unsigned recv_mask[kMaxLocalRanks][3];  // per hosted rank: ranks that send to it
+    int n_fwd;             // forward entries
+    int fwd_tiles;         // tiles to forward, all entries
+    unsigned send_mask[kMaxLocalRanks][3];  // per hosted rank: ranks it writes to (as master or as forwarder)
+    unsigned recv_mask[kMaxLocalRanks][3];  // per hosted rank: ranks that write to it
     int timeout_peer;
-    unsigned long long epoch;  // opened by the last CTA of the launch
+    int s_tile;
+    unsigned long long epoch;
+    int shard_tiles[4];
+    int w_a[kSyncThreads / 32], w_r[kSyncThreads / 32];
     short rep_start[kMaxExpertsPerDomain + 1];  // [n_active+1] offsets into dst_*
+    unsigned char relay_r[kMaxExpertsPerDomain];  // [n_active] 0: direct, else the replica count of a relayed expert
     // Addresses are resolved once per CTA: the issuing thread must not chase pointers
     // through global memory for every 32 KiB tile.
     const uint8_t* src[kMaxExpertsPerDomain][4];  // [n_active][shard] master shard base
     uint8_t* dst_weight[kMaxSends];               // replica slot base in the peer's weight buffer (null: skip)
     uint8_t* dst_scale[kMaxSends];                // replica slot base in the peer's scale buffer
+    uint64_t* dst_flags[kMaxSends];               // that slot's row of ready flags on the peer (relay)
     // replica buffer bases of every (hosted rank, peer): nlocal * N entries (at most 72: several
     // hosted ranks mean a simulated group of at most 8)
     uint8_t* peer_weight[kMaxPeers];
     uint8_t* peer_scale[kMaxPeers];
+    uint64_t* peer_flags[kMaxPeers];
+    // forward entries: one per local replica slot that holds a relayed expert
+    uint8_t* fwd_src_w[kMaxFwd];        // the slot itself
+    uint8_t* fwd_src_s[kMaxFwd];
+    const uint64_t* fwd_flags[kMaxFwd]; // its row of ready flags
+    unsigned char fwd_r[kMaxFwd], fwd_k[kMaxFwd], fwd_lr[kMaxFwd];
+    int fwd_tile_start[kMaxFwd + 1];    // prefix of the tiles each entry forwards
+    short fwd_dst_start[kMaxFwd + 1];
+    uint8_t* fwd_dst_w[kMaxFwdDst];
+    uint8_t* fwd_dst_s[kMaxFwdDst];
+    __align__(8) uint64_t bars[8];
 };
 
 struct TileRef {
-    int active;      // index into active_master
-    int shard;       // 0..3
-    int64_t offset;  // byte offset inside the shard
-    int bytes;       // bytes of this tile
+    int active;          // send tile: index of the active master; forward tile: -1 - entry
+    int tile_in_expert;  // tile index over the expert's shards
+    int shard;           // 0..3
+    int64_t offset;      // byte offset inside the shard
+    int bytes;           // bytes of this tile
 };
 
 template <int kSyncTile>
-__device__ __forceinline__ TileRef decode_tile(int64_t idx, int n_active, const ShardLayout& sh, const int* shard_tiles) {
-    TileRef t;
-    const int idx32 = static_cast<int>(idx);  // tile counts fit 32 bits (checked on the host side by construction)
-    t.active = idx32 % n_active;
-    int tile = idx32 / n_active;
+__device__ __forceinline__ void locate_tile(TileRef& t, const ShardLayout& sh, const int* shard_tiles) {
+    int tile = t.tile_in_expert;
     t.shard = 0;
     while (t.shard < sh.num_shards - 1 && tile >= shard_tiles[t.shard]) {
         tile -= shard_tiles[t.shard];
@@ -75,36 +101,68 @@ __device__ __forceinline__ TileRef decode_tile(int64_t idx, int n_active, const 
     t.offset = static_cast<int64_t>(tile) * kSyncTile;
     const int64_t left = sh.bytes[t.shard] - t.offset;
     t.bytes = static_cast<int>(left < kSyncTile ? left : kSyncTile);
+}
+
+// idx < send_tiles: tile idx / n_active of master idx % n_active. Above: the forward tiles, entry after entry.
+template <int kSyncTile, bool kRelay>
+__device__ __forceinline__ TileRef decode_tile(int idx, int send_tiles, const SyncShared& sm, const ShardLayout& sh) {
+    TileRef t;
+    if (!kRelay || idx < send_tiles) {
+        t.active = idx % sm.n_active;
+        t.tile_in_expert = idx / sm.n_active;
+    } else {
+        const int f_idx = idx - send_tiles;
+        int f = 0;
+        while (f + 1 < sm.n_fwd && f_idx >= sm.fwd_tile_start[f + 1]) ++f;
+        t.active = -1 - f;
+        t.tile_in_expert = sm.fwd_k[f] + (f_idx - sm.fwd_tile_start[f]) * sm.fwd_r[f];
+    }
+    locate_tile<kSyncTile>(t, sh, sm.shard_tiles);
     return t;
 }
 
-__device__ __forceinline__ uint8_t* dest_addr(const SyncShared& sm, const ShardLayout& sh, int shard, int rep) {
-    return (shard < 2 ? sm.dst_weight[rep] : sm.dst_scale[rep]) + sh.slot_offset[shard];
+__device__ __forceinline__ uint8_t* shard_base(uint8_t* weight_slot, uint8_t* scale_slot, const ShardLayout& sh, int shard) {
+    return (shard < 2 ? weight_slot : scale_slot) + sh.slot_offset[shard];
 }
 
-__device__ void copy_plain(const uint8_t* src, uint8_t* dst, int bytes) {
+// `streaming`: the source is read-only for the whole launch (a master). A forwarded tile was written
+// by a peer during this launch and must be read through L2.
+__device__ void copy_plain(const uint8_t* src, uint8_t* dst, int bytes, bool streaming) {
     const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
     int done = 0;
     if (vec) {
         const int nvec = bytes / 16;
         for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-            st_global_cs_v4(dst + static_cast<int64_t>(i) * 16, ld_global_nc_v4(src + static_cast<int64_t>(i) * 16));
+            const void* p = src + static_cast<int64_t>(i) * 16;
+            st_global_cs_v4(dst + static_cast<int64_t>(i) * 16, streaming ? ld_global_nc_v4(p) : ld_global_cg_v4(p));
         }
         done = nvec * 16;
     }
-    for (int i = done + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
+    for (int i = done + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = streaming ? src[i] : __ldcg(src + i);
 }
 
-template <int kSyncTile, int kSyncStages>
+__device__ __forceinline__ bool relayed(int reps, int relay_min) {
+    return relay_min > 0 && reps >= relay_min && reps >= 2 && reps <= kMaxRelayReplicas;
+}
+
+// kRelay = false compiles the relay machinery out: the direct fan-out pays neither for its code nor for
+// its per-tile bookkeeping (the kernel runs once per layer from a cold instruction cache, and the one
+// issuing thread per CTA is on the critical path of every tile).
+template <int kSyncTile, int kSyncStages, bool kRelay>
 __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call) {
-    extern __shared__ __align__(128) char smem_raw[];  // kSyncStages * kSyncTile
-    __shared__ SyncShared sm;
-    __shared__ __align__(8) uint64_t bars[kSyncStages];
-    __shared__ int shard_tiles[4];
+    extern __shared__ __align__(128) char smem_raw[];  // kSyncStages * kSyncTile, then SyncShared
+    SyncShared& sm = *reinterpret_cast<SyncShared*>(smem_raw + static_cast<size_t>(kSyncStages) * kSyncTile);
+    uint64_t* bars = sm.bars;
+    int* shard_tiles = sm.shard_tiles;
 
     const ShardLayout& sh = call.shards;
     const int M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N, nlocal = call.nlocal;
     const int tid = threadIdx.x;
+    // Relaying needs a forward entry per local replica slot; the limit depends on the configuration
+    // only, so every rank comes to the same answer.
+    int tiles_per_expert = 0;
+    for (int s = 0; s < sh.num_shards; ++s) tiles_per_expert += static_cast<int>((sh.bytes[s] + kSyncTile - 1) / kSyncTile);
+    const int relay_min = (kRelay && nlocal * R <= kMaxFwd && tiles_per_expert <= call.relay_cap) ? call.relay_min_replicas : 0;
     auto stamp = [&](int slot) {
         if (call.trace != nullptr && tid == 0) call.trace[blockIdx.x * 8 + slot] = global_timer_ns();
     };
@@ -116,6 +174,8 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         sm.total_reps = 0;
         sm.all_aligned = 1;
         sm.is_last = 0;
+        sm.n_fwd = 0;
+        sm.fwd_tiles = 0;
         sm.timeout_peer = -1;
         for (int s = 0; s < 4; ++s) shard_tiles[s] = s < sh.num_shards ? static_cast<int>((sh.bytes[s] + kSyncTile - 1) / kSyncTile) : 0;
         for (int s = 0; s < kSyncStages; ++s) mbar_init(&bars[s], 1);
@@ -150,17 +210,25 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         }
     }
     uint8_t *pre_pw = nullptr, *pre_ps = nullptr;
+    uint64_t* pre_pf = nullptr;
     if (tid < nlocal * N) {
         const RankDev& rk = *call.rank[tid / N];
         pre_pw = rk.peer_replica_weight[tid % N];
         pre_ps = rk.peer_replica_scale[tid % N];
+        if (kRelay) pre_pf = rk.peer_relay_flags[tid % N];
     }
+    // Ranks hosted together share the first one's epoch counter: they always run in the same launches.
+    // The CTA that finishes last stores the new value; nobody reads the counter after that.
+    unsigned long long pre_epoch = 0;
+    if (tid == 0) pre_epoch = *call.sync_epoch;
     int pre_owner = -1;
     if (tid < nlocal * R) pre_owner = call.plan[tid / R].p2l[call.my_rank[tid / R] * Lp + M + tid % R];
     if (tid < nlocal * N) {
         sm.peer_weight[tid] = pre_pw;
         sm.peer_scale[tid] = pre_ps;
+        sm.peer_flags[tid] = pre_pf;
     }
+    if (tid == 0) sm.epoch = pre_epoch + 1;
     // (the scan below synchronises the CTA before the tables are read)
 
     // blocked scan over (hosted rank, master): active index and replica offsets
@@ -188,21 +256,21 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                 r_incl += orr;
             }
         }
-        __shared__ int w_a[kSyncThreads / 32], w_r[kSyncThreads / 32];
         if (lane == 31) {
-            w_a[warp] = a_incl;
-            w_r[warp] = r_incl;
+            sm.w_a[warp] = a_incl;
+            sm.w_r[warp] = r_incl;
         }
         __syncthreads();
         int a_off = sm.n_active, r_off = sm.total_reps;
         for (int w = 0; w < warp; ++w) {
-            a_off += w_a[w];
-            r_off += w_r[w];
+            a_off += sm.w_a[w];
+            r_off += sm.w_r[w];
         }
         if (act) {
             const int ai = a_off + a_incl - 1;
             const int rs = r_off + r_incl - reps;
             sm.rep_start[ai] = static_cast<short>(rs);
+            if (kRelay) sm.relay_r[ai] = relayed(reps, relay_min) ? static_cast<unsigned char>(reps) : 0;
             const int l = me * M + m;
             auto place = [&](int j, int phys) {
                 const int drank = phys / Lp, dslot = phys % Lp - M;
@@ -210,10 +278,12 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                     report_error(rk.status, UEP_DEV_BAD_PLAN, l);
                     sm.dst_weight[rs + j] = nullptr;
                     sm.dst_scale[rs + j] = nullptr;
+                    if (kRelay) sm.dst_flags[rs + j] = nullptr;
                 } else {
                     atomicOr(&sm.send_mask[lr][drank >> 5], 1u << (drank & 31));
                     sm.dst_weight[rs + j] = sm.peer_weight[lr * N + drank] + static_cast<int64_t>(dslot) * sh.weight_slot_stride;
                     sm.dst_scale[rs + j] = sm.peer_scale[lr * N + drank] + static_cast<int64_t>(dslot) * sh.scale_slot_stride;
+                    if (kRelay) sm.dst_flags[rs + j] = sm.peer_flags[lr * N + drank] + static_cast<int64_t>(dslot) * call.relay_cap;
                 }
             };
             if (g0 == 0 && row_cached) {
@@ -246,6 +316,9 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         __syncthreads();
     }
     if (tid == 0) sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxSends ? sm.total_reps : kMaxSends);
+    // Owners of the local replica slots: who sends to this rank; and, for relayed experts, what this
+    // rank forwards. One thread per (hosted rank, slot).
+    int my_fwd_r = 0, my_fwd_k = -1, my_l = -1;
     for (int i = tid; i < nlocal * R; i += blockDim.x) {
         const int lr = i / R, slot = i % R;
         const int me = call.my_rank[lr];
@@ -253,103 +326,270 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         if (l >= 0) {
             const int src = l / M;
             if (src >= 0 && src < N && src != me) atomicOr(&sm.recv_mask[lr][src >> 5], 1u << (src & 31));
+            if (kRelay && relay_min > 0 && i == tid && l < N * M) {  // nlocal * R <= kMaxFwd <= blockDim.x: one pass
+                const int reps = min(max(call.plan[lr].lcnts[l] - 1, 0), D - 1);
+                if (relayed(reps, relay_min)) {
+                    const int mine = me * Lp + M + slot;
+                    for (int j = 0; j < reps; ++j) {
+                        if (call.plan[lr].l2p[static_cast<int64_t>(l) * D + 1 + j] == mine) my_fwd_k = j;
+                    }
+                    if (my_fwd_k >= 0) {
+                        my_fwd_r = reps;
+                        my_l = l;
+                    }
+                }
+            }
+        }
+    }
+    if (kRelay && relay_min > 0) {
+        // compact the forward entries (thread order = slot order) and lay out their destination lists
+        const unsigned has = __ballot_sync(kFullMask, my_fwd_r > 0);
+        const int lane = tid & 31, warp = tid >> 5;
+        if (lane == 0) sm.w_a[warp] = __popc(has);
+        __syncthreads();
+        int f = __popc(has & ((1u << lane) - 1u));
+        for (int w = 0; w < warp; ++w) f += sm.w_a[w];
+        if (my_fwd_r > 0) {
+            const int lr = tid / R, slot = tid % R;
+            const int me = call.my_rank[lr];
+            sm.fwd_src_w[f] = sm.peer_weight[lr * N + me] + static_cast<int64_t>(slot) * sh.weight_slot_stride;
+            sm.fwd_src_s[f] = sm.peer_scale[lr * N + me] + static_cast<int64_t>(slot) * sh.scale_slot_stride;
+            sm.fwd_flags[f] = sm.peer_flags[lr * N + me] + static_cast<int64_t>(slot) * call.relay_cap;
+            sm.fwd_r[f] = static_cast<unsigned char>(my_fwd_r);
+            sm.fwd_k[f] = static_cast<unsigned char>(my_fwd_k);
+            sm.fwd_lr[f] = static_cast<unsigned char>(lr);
+            // tiles k, k + r, k + 2r, ... of the expert
+            sm.fwd_tile_start[f + 1] = tiles_per_expert > my_fwd_k ? (tiles_per_expert - my_fwd_k + my_fwd_r - 1) / my_fwd_r : 0;
+            sm.fwd_dst_start[f + 1] = static_cast<short>(my_fwd_r - 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int nf = 0;
+            for (int w = 0; w < kSyncThreads / 32; ++w) nf += sm.w_a[w];
+            sm.fwd_tile_start[0] = 0;
+            sm.fwd_dst_start[0] = 0;
+            for (int e = 0; e < nf; ++e) {
+                sm.fwd_tile_start[e + 1] += sm.fwd_tile_start[e];
+                sm.fwd_dst_start[e + 1] = static_cast<short>(sm.fwd_dst_start[e + 1] + sm.fwd_dst_start[e]);
+            }
+            sm.n_fwd = nf;
+            sm.fwd_tiles = sm.fwd_tile_start[nf];
+        }
+        __syncthreads();
+        if (my_fwd_r > 0) {
+            const int lr = tid / R;
+            const int me = call.my_rank[lr];
+            int o = sm.fwd_dst_start[f];
+            for (int j = 0; j < my_fwd_r; ++j) {
+                const int phys = call.plan[lr].l2p[static_cast<int64_t>(my_l) * D + 1 + j];
+                const int drank = phys / Lp, dslot = phys % Lp - M;
+                const bool bad = phys < 0 || drank >= N || dslot < 0 || dslot >= R;
+                if (!bad && drank != me) atomicOr(&sm.recv_mask[lr][drank >> 5], 1u << (drank & 31));  // it forwards to me
+                if (j == my_fwd_k) continue;
+                if (bad) {
+                    sm.fwd_dst_w[o] = nullptr;
+                    sm.fwd_dst_s[o] = nullptr;
+                } else {
+                    atomicOr(&sm.send_mask[lr][drank >> 5], 1u << (drank & 31));
+                    sm.fwd_dst_w[o] = sm.peer_weight[lr * N + drank] + static_cast<int64_t>(dslot) * sh.weight_slot_stride;
+                    sm.fwd_dst_s[o] = sm.peer_scale[lr * N + drank] + static_cast<int64_t>(dslot) * sh.scale_slot_stride;
+                }
+                ++o;
+            }
         }
     }
     __syncthreads();
 
     stamp(1);
     // ---- copy -------------------------------------------------------------------------
-    int tiles_per_expert = 0;
-    for (int s = 0; s < sh.num_shards; ++s) tiles_per_expert += shard_tiles[s];
-    const int total_tiles = sm.n_active * tiles_per_expert;
+    const int send_tiles = sm.n_active * tiles_per_expert;
+    const int total_tiles = send_tiles + sm.fwd_tiles;
+    const uint64_t epoch = sm.epoch;
     DeviceStatus* status0 = call.rank[0]->status;
     // Tiles are handed out by an atomic counter: CTAs that run on busy SMs (the reroute and the
     // model's own kernels run next to this one) simply take fewer, and replica counts that differ
     // between masters cannot leave some CTAs with several times the work of others.
     int* tile_counter = call.rank[0]->sync_ticket + 1;
 
+    // Source of a tile. A forward tile first waits (bounded) until the master has delivered it here.
+    auto tile_source = [&](const TileRef& t, bool& ok) -> const uint8_t* {
+        if (!kRelay || t.active >= 0) return sm.src[t.active][t.shard] + t.offset;
+        const int f = -1 - t.active;
+        if (!wait_flag_ge_relaxed(sm.fwd_flags[f] + t.tile_in_expert, epoch, call.timeout_ns)) {
+            ok = false;
+            report_error(call.rank[sm.fwd_lr[f]]->status, UEP_DEV_TIMEOUT_SYNC, t.tile_in_expert);
+        }
+        __threadfence_system();        // acquire side of the flag
+        fence_proxy_async_global();    // ... also for the bulk copy that reads the tile next
+        return shard_base(sm.fwd_src_w[f], sm.fwd_src_s[f], sh, t.shard) + t.offset;
+    };
+    // Destinations of a tile: d = 0 .. count-1 -> address (null: skip). For a relayed send tile the single
+    // destination is replica (tile mod r), and `flag` is that replica's ready flag for the tile.
+    auto dest_range = [&](const TileRef& t, int& first, int& count, uint64_t*& flag) {
+        flag = nullptr;
+        if (t.active >= 0) {
+            const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
+            const int rr = kRelay ? sm.relay_r[t.active] : 0;
+            if (rr == 0) {
+                first = r0;
+                count = r1 - r0;
+            } else {
+                first = r0 + t.tile_in_expert % rr;
+                count = first < r1 ? 1 : 0;
+                if (count && sm.dst_flags[first] != nullptr) flag = sm.dst_flags[first] + t.tile_in_expert;
+            }
+        } else {
+            const int f = -1 - t.active;
+            first = sm.fwd_dst_start[f];
+            count = sm.fwd_dst_start[f + 1] - first;
+        }
+    };
+    auto dest_addr = [&](const TileRef& t, int d) -> uint8_t* {
+        uint8_t* w = (!kRelay || t.active >= 0) ? sm.dst_weight[d] : sm.fwd_dst_w[d];
+        if (w == nullptr) return nullptr;
+        uint8_t* s = (!kRelay || t.active >= 0) ? sm.dst_scale[d] : sm.fwd_dst_s[d];
+        return shard_base(w, s, sh, t.shard) + t.offset;
+    };
+
     if (sm.all_aligned) {
         if (tid == 0) {
-            int ring_tile[kSyncStages];  // tile index held by each stage (>= total_tiles: none)
+            int ring_tile[kSyncStages];        // tile index held by each stage (>= total_tiles: none)
+            uint64_t* flag_ring[kSyncStages];  // ready flag owed for the k-th stored tile, slot k % stages
+            uint32_t phase_bits = 0;           // bit s: parity the next wait on stage s expects
+            bool ok = true;
             // The index of the next tile is requested one load ahead, so the round trip of the
             // atomic overlaps with the copies instead of sitting in front of every load.
             int pending = atomicAdd(tile_counter, 1);
-            auto issue_load = [&](int s) {
-                const int idx = pending;
-                pending = idx < total_tiles ? atomicAdd(tile_counter, 1) : idx;
-                ring_tile[s] = idx;
-                if (idx >= total_tiles) return;
-                const TileRef t = decode_tile<kSyncTile>(idx, sm.n_active, sh, shard_tiles);
-                const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
-                const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
-                if (bytes16) {
-                    mbar_expect_tx(&bars[s], bytes16);
-                    bulk_load(smem_raw + s * kSyncTile, src, bytes16, &bars[s]);
-                }
-            };
 #pragma unroll
-            for (int s = 0; s < kSyncStages; ++s) ring_tile[s] = total_tiles;
+            for (int s = 0; s < kSyncStages; ++s) flag_ring[s] = nullptr;
+            // Two passes over the same ring: first the send tiles, then the forward tiles. A CTA must
+            // not wait for a ready flag while it still holds send tiles it has loaded but not stored,
+            // or ready flags it has not raised: another CTA (here or on a peer) may be waiting for
+            // exactly those. So the first pass stops at the first forward tile, drains, raises its
+            // flags, and only the second pass waits.
+            for (int pass = 0; pass < (kRelay ? 2 : 1); ++pass) {
+                const int limit = pass == 0 ? send_tiles : total_tiles;
+                if (pending >= limit) continue;
+                auto issue_load = [&](int s) {
+                    const int idx = pending;
+                    ring_tile[s] = idx < limit ? idx : total_tiles;
+                    if (idx >= limit) return;  // keeps `pending`: a claimed forward tile waits for the second pass
+                    pending = atomicAdd(tile_counter, 1);
+                    const TileRef t = decode_tile<kSyncTile, kRelay>(idx, send_tiles, sm, sh);
+                    const uint8_t* src = tile_source(t, ok);
+                    const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
+                    if (bytes16) {
+                        mbar_expect_tx(&bars[s], bytes16);
+                        bulk_load(smem_raw + s * kSyncTile, src, bytes16, &bars[s]);
+                    }
+                };
 #pragma unroll
-            for (int s = 0; s < kSyncStages - 1; ++s) issue_load(s);
-            uint32_t phase_bits = 0;  // bit s: parity the next wait on stage s expects
-            bool ok = true;
-            int k = 0;
-            while (true) {
-                const int s = k % kSyncStages;
-                const int idx = ring_tile[s];
-                if (idx >= total_tiles) break;  // indices are handed out in order: nothing is left
-                const TileRef t = decode_tile<kSyncTile>(idx, sm.n_active, sh, shard_tiles);
-                const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
-                if (bytes16) {
-                    if (!mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns)) {
-                        ok = false;
-                        break;
+                for (int s = 0; s < kSyncStages; ++s) ring_tile[s] = total_tiles;
+#pragma unroll
+                for (int s = 0; s < kSyncStages - 1; ++s) issue_load(s);
+                int k = 0;
+                while (true) {
+                    const int s = k % kSyncStages;
+                    const int idx = ring_tile[s];
+                    if (idx >= total_tiles) break;  // indices are handed out in order: nothing is left for this pass
+                    const TileRef t = decode_tile<kSyncTile, kRelay>(idx, send_tiles, sm, sh);
+                    const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
+                    if (bytes16) {
+                        if (!mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns)) {
+                            ok = false;
+                            report_error(status0, UEP_DEV_TIMEOUT_COPY, k);
+                            ring_tile[s] = total_tiles;
+                            break;
+                        }
+                        phase_bits ^= 1u << s;
                     }
-                    phase_bits ^= 1u << s;
+                    ring_tile[s] = total_tiles;
+                    int first, count;
+                    uint64_t* flag;
+                    dest_range(t, first, count, flag);
+                    for (int d = first; d < first + count; ++d) {
+                        uint8_t* dst = dest_addr(t, d);
+                        if (dst == nullptr) continue;
+                        if (bytes16) bulk_store(dst, smem_raw + s * kSyncTile, bytes16);
+                        if (static_cast<uint32_t>(t.bytes) != bytes16) {  // up to 15 trailing bytes of a shard
+                            const uint8_t* src =
+                                (!kRelay || t.active >= 0) ? sm.src[t.active][t.shard] + t.offset
+                                              : shard_base(sm.fwd_src_w[-1 - t.active], sm.fwd_src_s[-1 - t.active], sh, t.shard) + t.offset;
+                            for (int b = bytes16; b < t.bytes; ++b) dst[b] = __ldcg(src + b);
+                        }
+                    }
+                    bulk_commit();
+                    // A relayed tile's ready flag may go out once its stores are complete, not merely read:
+                    // the flag of the tile stored kSyncStages-1 iterations ago is due now.
+                    if (kRelay) {
+                        uint64_t* due = flag_ring[(k + 1) % kSyncStages];
+                        flag_ring[(k + 1) % kSyncStages] = nullptr;
+                        flag_ring[s] = flag;
+                        if (due != nullptr) {
+                            bulk_wait_all<kSyncStages - 1>();
+                            st_release_sys_u64(due, epoch);
+                        }
+                    }
+                    // refill the stage that the previous tile's stores have finished reading
+                    const int refill = (k + kSyncStages - 1) % kSyncStages;
+                    if (k >= 1) bulk_wait_read<1>();
+                    issue_load(refill);
+                    ++k;
                 }
-                const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
-                for (int r = r0; r < r1; ++r) {
-                    if (sm.dst_weight[r] == nullptr) continue;
-                    uint8_t* dst = dest_addr(sm, sh, t.shard, r) + t.offset;
-                    if (bytes16) bulk_store(dst, smem_raw + s * kSyncTile, bytes16);
-                    if (static_cast<uint32_t>(t.bytes) != bytes16) {  // up to 15 trailing bytes of a shard
-                        const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
-                        for (int b = bytes16; b < t.bytes; ++b) dst[b] = src[b];
+                if (pass == 0) stamp(2);
+                bulk_wait_all<0>();
+                bool any_flag = false;
+                if (kRelay) {
+#pragma unroll
+                    for (int s = 0; s < kSyncStages; ++s) any_flag |= flag_ring[s] != nullptr;
+                }
+                if (any_flag) {
+                    __threadfence_system();
+#pragma unroll
+                    for (int s = 0; s < kSyncStages; ++s) {
+                        if (flag_ring[s] != nullptr) st_relaxed_sys_u64(flag_ring[s], epoch);
+                        flag_ring[s] = nullptr;
                     }
                 }
-                bulk_commit();
-                // refill the stage that the previous tile's stores have finished reading
-                const int refill = (k + kSyncStages - 1) % kSyncStages;
-                if (k >= 1) bulk_wait_read<1>();
-                issue_load(refill);
-                ++k;
+                if (!ok) {
+                    // loads still in flight must land before the shared memory is released or reused
+                    for (int s = 0; s < kSyncStages; ++s) {
+                        if (ring_tile[s] < total_tiles) mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns);
+                    }
+                    break;
+                }
             }
-            stamp(2);
-            bulk_wait_all<0>();
             stamp(3);
-            if (!ok) {
-                report_error(status0, UEP_DEV_TIMEOUT_COPY, k);
-                // loads still in flight must land before the shared memory is released
-                for (int j = 0; j < kSyncStages; ++j) {
-                    const int s = (k + j) % kSyncStages;
-                    if (ring_tile[s] < total_tiles) mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns);
-                }
-            }
         }
     } else {
-        __shared__ int s_tile;
         while (true) {
             __syncthreads();
-            if (tid == 0) s_tile = atomicAdd(tile_counter, 1);
+            if (tid == 0) sm.s_tile = atomicAdd(tile_counter, 1);
             __syncthreads();
-            const int idx = s_tile;
+            const int idx = sm.s_tile;
             if (idx >= total_tiles) break;
-            const TileRef t = decode_tile<kSyncTile>(idx, sm.n_active, sh, shard_tiles);
-            const uint8_t* src = sm.src[t.active][t.shard] + t.offset;
-            const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
-            for (int r = r0; r < r1; ++r) {
-                if (sm.dst_weight[r] == nullptr) continue;
-                copy_plain(src, dest_addr(sm, sh, t.shard, r) + t.offset, t.bytes);
+            const TileRef t = decode_tile<kSyncTile, kRelay>(idx, send_tiles, sm, sh);
+            if (kRelay && t.active < 0) {  // forward tile: one thread waits for the master's delivery
+                if (tid == 0) {
+                    bool ok = true;
+                    (void)tile_source(t, ok);
+                }
+                __syncthreads();
+            }
+            const uint8_t* src = (!kRelay || t.active >= 0)
+                                     ? sm.src[t.active][t.shard] + t.offset
+                                     : shard_base(sm.fwd_src_w[-1 - t.active], sm.fwd_src_s[-1 - t.active], sh, t.shard) + t.offset;
+            int first, count;
+            uint64_t* flag;
+            dest_range(t, first, count, flag);
+            for (int d = first; d < first + count; ++d) {
+                uint8_t* dst = dest_addr(t, d);
+                if (dst != nullptr) copy_plain(src, dst, t.bytes, !kRelay || t.active >= 0);
+            }
+            if (flag != nullptr) {  // every thread's stores, then the flag
+                __threadfence_system();
+                __syncthreads();
+                if (tid == 0) st_release_sys_u64(flag, epoch);
             }
         }
     }
@@ -371,9 +611,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             *ticket_ptr = 0;
             *tile_counter = 0;  // every CTA has stopped taking tiles
             sm.is_last = 1;
-            // ranks hosted together share the first one's counter: they always run in the same launches
-            sm.epoch = call.rank[0]->epochs[1] + 1;
-            call.rank[0]->epochs[1] = sm.epoch;
+            *call.sync_epoch = epoch;  // this launch's epoch is closed
         }
     }
     __syncthreads();
@@ -395,7 +633,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                 if (me == call.withhold_rank) continue;
                 const RankDev& rk = *call.rank[lr];
                 for (int p = 0; p < N; ++p) {
-                    if (sm.send_mask[lr][p >> 5] & (1u << (p & 31))) st_relaxed_sys_u64(rk.peer_sync_flags[p] + me, sm.epoch);
+                    if (sm.send_mask[lr][p >> 5] & (1u << (p & 31))) st_relaxed_sys_u64(rk.peer_sync_flags[p] + me, epoch);
                 }
             }
         }
@@ -404,7 +642,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             const int lr = i / N, p = i % N;
             if (sm.recv_mask[lr][p >> 5] & (1u << (p & 31))) {
                 const RankDev& rk = *call.rank[lr];
-                if (!wait_flag_ge_relaxed(rk.peer_sync_flags[call.my_rank[lr]] + p, sm.epoch, call.timeout_ns)) {
+                if (!wait_flag_ge_relaxed(rk.peer_sync_flags[call.my_rank[lr]] + p, epoch, call.timeout_ns)) {
                     atomicMax(&sm.timeout_peer, p);
                     report_error(rk.status, UEP_DEV_TIMEOUT_SYNC, p);
                 }
@@ -421,16 +659,15 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
 // (tuning aid).
 struct SyncGeometry {
     int tile_kib, stages;
-    const void* fn;
+    const void* fn;        // direct fan-out only
+    const void* fn_relay;  // with the relay machinery
 };
-const SyncGeometry kGeometries[] = {
-    {32, 4, reinterpret_cast<const void*>(weight_sync_kernel<32 * 1024, 4>)},
-    {16, 4, reinterpret_cast<const void*>(weight_sync_kernel<16 * 1024, 4>)},
-    {16, 8, reinterpret_cast<const void*>(weight_sync_kernel<16 * 1024, 8>)},
-    {8, 8, reinterpret_cast<const void*>(weight_sync_kernel<8 * 1024, 8>)},
-    {32, 6, reinterpret_cast<const void*>(weight_sync_kernel<32 * 1024, 6>)},
-    {64, 3, reinterpret_cast<const void*>(weight_sync_kernel<64 * 1024, 3>)},
-};
+#define UEP_SYNC_VARIANT(T, S)                                                        \
+    {T, S, reinterpret_cast<const void*>(weight_sync_kernel<T * 1024, S, false>), \
+     reinterpret_cast<const void*>(weight_sync_kernel<T * 1024, S, true>)}
+const SyncGeometry kGeometries[] = {UEP_SYNC_VARIANT(32, 4), UEP_SYNC_VARIANT(16, 4), UEP_SYNC_VARIANT(16, 8),
+                                    UEP_SYNC_VARIANT(8, 8)};
+#undef UEP_SYNC_VARIANT
 
 const SyncGeometry& sync_geometry() {
     static const SyncGeometry* chosen = nullptr;
@@ -448,34 +685,44 @@ const SyncGeometry& sync_geometry() {
     return *chosen;
 }
 
+size_t sync_smem_bytes(const SyncGeometry& g) {
+    return static_cast<size_t>(g.stages) * g.tile_kib * 1024 + sizeof(SyncShared);
+}
+
 }  // namespace
 
 int weight_sync_max_ctas_per_rank(int nlocal, int num_sms) {
     // CTAs that fit one wave: shared memory bounds the CTAs per SM; hosted ranks share the device
-    const SyncGeometry& g = sync_geometry();
-    const int smem = g.tile_kib * 1024 * g.stages + 30 * 1024;
-    int per_sm = (227 * 1024) / smem;
+    const size_t smem = sync_smem_bytes(sync_geometry()) + 1024;
+    int per_sm = static_cast<int>((227 * 1024) / smem);
     per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
     const int per = num_sms * per_sm / (nlocal > 0 ? nlocal : 1);
     return per < 1 ? 1 : per;
 }
 
+int weight_sync_tile_bytes() { return sync_geometry().tile_kib * 1024; }
+
 cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream) {
     const SyncGeometry& g = sync_geometry();
-    const size_t smem = static_cast<size_t>(g.stages) * g.tile_kib * 1024;
-    static const void* attr_set_for = nullptr;
-    if (attr_set_for != g.fn) {
-        cudaError_t e = cudaFuncSetAttribute(g.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    const size_t smem = sync_smem_bytes(g);
+    const bool relay = call.relay_min_replicas > 0;
+    const void* fn = relay ? g.fn_relay : g.fn;
+    static const void* attr_set_for[2] = {nullptr, nullptr};
+    if (attr_set_for[relay] != fn) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        attr_set_for = g.fn;
+        attr_set_for[relay] = fn;
     }
-    // Hosted ranks pool their tiles over all CTAs. The only waits are those of the last CTA,
-    // on flags that peers on other devices (or, for hosted ranks, this very CTA) write.
+    // Hosted ranks pool their tiles over all CTAs. Without relaying, the only waits are those of the
+    // last CTA, on flags that peers on other devices write. With relaying, CTAs that forward wait for
+    // CTAs that send; when both are in this launch (ranks hosted together) they must be co-resident,
+    // which a cooperative launch guarantees.
     const dim3 grid(call.nlocal * call.ctas_per_rank), block(kSyncThreads);
     count_launch();
     SyncCall copy = call;
     void* args[] = {&copy};
-    cudaError_t e = cudaLaunchKernel(g.fn, grid, block, args, smem, stream);
+    cudaError_t e = (call.nlocal > 1 && relay) ? cudaLaunchCooperativeKernel(fn, grid, block, args, smem, stream)
+                                               : cudaLaunchKernel(fn, grid, block, args, smem, stream);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 

@@ -96,7 +96,10 @@ class Manager:
         self.quota_kernel_stage = tuning.quota_kernel_stage
         self.quota_reroute_interleave = tuning.quota_reroute_interleave
         plan_mode, plan_mode_id = tuning.weight_sync_plan_mode, tuning.weight_sync_plan_mode_id
-        if self.nvl_domain_size <= 8 and plan_mode != "direct":
+        # As in the reference, the default (adaptive) falls back to the direct fan-out when the NVLink
+        # domain has at most 8 ranks. An explicit force_relay is honoured at any size: here relaying is
+        # scatter + replica-to-replica forward inside the one copy kernel, not a second stage.
+        if self.nvl_domain_size <= 8 and plan_mode == "adaptive":
             if self.rank == 0:
                 print(f"UltraEP: NVL domain size <= 8; forcing weight_sync plan mode to direct (was {plan_mode}).",
                       flush=True)

@@ -64,7 +64,8 @@ def make_config(num_ranks: int, masters: int, redundant: int, num_layers: int = 
                 fc2_numel: int = 0, weight_elem_bytes: int = 2, scale_elem_bytes: int = 1, fc1_scale_numel: int = 0,
                 fc2_scale_numel: int = 0, is_train: bool = True, rank: int = 0, sim: bool = False,
                 solver: Optional[capi.SolverParams] = None, grad_reduce_num_sms: int = 42,
-                weight_sync_num_sms: int = 0, wait_timeout_ms: int = 0) -> capi.Config:
+                weight_sync_num_sms: int = 0, wait_timeout_ms: int = 0, plan_mode: int = 0,
+                relay_min_replicas: int = 4) -> capi.Config:
     cfg = capi.Config()
     cfg.num_ranks = num_ranks
     cfg.nvl_ranks = num_ranks
@@ -86,8 +87,8 @@ def make_config(num_ranks: int, masters: int, redundant: int, num_layers: int = 
     cfg.quota_kernel_stage = 1
     cfg.grad_reduce_num_sms = grad_reduce_num_sms
     cfg.grad_reduce_deterministic = 1
-    cfg.weight_sync_plan_mode = 0
-    cfg.weight_sync_relay_min_replicas = 4
+    cfg.weight_sync_plan_mode = plan_mode
+    cfg.weight_sync_relay_min_replicas = relay_min_replicas
     cfg.weight_sync_relay_max_relays = 8
     cfg.weight_sync_relay_min_fanout_gain = 2
     cfg.weight_sync_num_sms = weight_sync_num_sms
