@@ -352,6 +352,98 @@ void uep_oracle_init_master_placement(int32_t* p2l, int32_t* l2p, int32_t* lcnts
     }
 }
 
+// csrc/kernels/legacy/placement_cpu.cpp:17-172 — the host-side solver of legacy_placement=True, per
+// NVLink domain: (1) redundant slots are granted one at a time to the expert with the largest load per
+// instance (ties: lower id; an expert gets at most G-1 extra instances; with balance_threshold > 1 the
+// granting stops once the best load per instance is within threshold x the mean load per master slot);
+// (2) the extra instances, ordered by load per instance descending then expert id, go to the rank with the
+// smallest accumulated load (ties: lower rank) that has a free slot and does not hold the expert yet; an
+// instance that finds no rank is dropped. Loads per instance are doubles, as in the reference. Quotas are
+// not used in this mode (the reroute is round-robin), the caller zeroes them (:235-240).
+void uep_oracle_legacy_solve_placement(const int32_t* expert_loads, int32_t* p2l, int32_t* l2p, int32_t* lcnts,
+                                       int num_ranks, int M, int R, int nvl_ranks, int D, float balance_threshold) {
+    const int Lp = M + R, L = num_ranks * M, P = num_ranks * Lp, E = nvl_ranks * M;
+    std::fill(p2l, p2l + P, -1);
+    std::fill(l2p, l2p + static_cast<int64_t>(L) * D, -1);
+    for (int l = 0; l < L; ++l) {
+        const int phys = (l / M) * Lp + l % M;
+        p2l[phys] = l;
+        l2p[static_cast<int64_t>(l) * D] = phys;
+        lcnts[l] = 1;
+    }
+    if (R == 0 || nvl_ranks <= 1) return;
+    for (int dom = 0; dom < num_ranks / nvl_ranks; ++dom) {
+        const int rank0 = dom * nvl_ranks, log0 = rank0 * M;
+        double total = 0.0;
+        for (int e = 0; e < E; ++e) total += expert_loads[log0 + e];
+        const double mean_per_slot = total > 0.0 ? total / (nvl_ranks * M) : 0.0;
+        // (1) how many instances each expert gets
+        for (int slot = 0; slot < nvl_ranks * R; ++slot) {
+            int best = -1;
+            double best_score = -1.0;
+            for (int e = 0; e < E; ++e) {
+                const int l = log0 + e;
+                if (lcnts[l] - 1 >= nvl_ranks - 1) continue;
+                const double score = static_cast<double>(expert_loads[l]) / lcnts[l];
+                if (score > best_score) {  // equal scores keep the lower id (ascending scan)
+                    best_score = score;
+                    best = l;
+                }
+            }
+            if (balance_threshold > 1.0f && mean_per_slot > 0.0 && best_score <= mean_per_slot * balance_threshold) break;
+            if (best < 0) break;
+            lcnts[best] += 1;
+        }
+        // (2) where the extra instances live
+        struct Extra {
+            int l;
+            double per_instance;
+        };
+        std::vector<Extra> extras;
+        for (int e = 0; e < E; ++e) {
+            const int l = log0 + e;
+            for (int j = 1; j < lcnts[l]; ++j) extras.push_back({l, static_cast<double>(expert_loads[l]) / lcnts[l]});
+        }
+        std::stable_sort(extras.begin(), extras.end(), [](const Extra& a, const Extra& b) {
+            return a.per_instance != b.per_instance ? a.per_instance > b.per_instance : a.l < b.l;
+        });
+        std::vector<double> rank_load(nvl_ranks, 0.0);
+        std::vector<int> used(nvl_ranks, 0);
+        std::vector<char> holds(static_cast<size_t>(nvl_ranks) * E, 0);
+        for (int r = 0; r < nvl_ranks; ++r) {
+            for (int m = 0; m < M; ++m) {
+                const int l = (rank0 + r) * M + m;
+                rank_load[r] += static_cast<double>(expert_loads[l]) / lcnts[l];
+                holds[static_cast<size_t>(r) * E + r * M + m] = 1;
+            }
+        }
+        for (const Extra& x : extras) {
+            const int e = x.l - log0;
+            int target = -1;
+            for (int r = 0; r < nvl_ranks; ++r) {
+                if (used[r] >= R || holds[static_cast<size_t>(r) * E + e]) continue;
+                if (target < 0 || rank_load[r] < rank_load[target]) target = r;
+            }
+            if (target < 0) {
+                lcnts[x.l] -= 1;
+                continue;
+            }
+            const int phys = (rank0 + target) * Lp + M + used[target];
+            p2l[phys] = x.l;
+            int32_t* row = l2p + static_cast<int64_t>(x.l) * D;
+            for (int j = 1; j < D; ++j) {
+                if (row[j] == -1) {
+                    row[j] = phys;
+                    break;
+                }
+            }
+            rank_load[target] += x.per_instance;
+            used[target] += 1;
+            holds[static_cast<size_t>(target) * E + e] = 1;
+        }
+    }
+}
+
 // csrc/kernels/placement.cu:788-1482 (kernel) and :1561-1663 (pre-clears + launch).
 // Returns 0 on success; -1 on a parameter outside the reference's static limits
 // (:1589-1597); -2 if the final rebuild is infeasible (the reference traps, :1277).

@@ -52,6 +52,7 @@ def lib() -> C.CDLL:
         + [C.c_float, C.c_int32, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_void_p]
     )
     L.uep_oracle_solve_placement.restype = C.c_int
+    L.uep_oracle_legacy_solve_placement.argtypes = [_i32p] * 4 + [C.c_int] * 5 + [C.c_float]
     L.uep_oracle_dense_reroute_forward.argtypes = [_u8p, _f32p, _i32p, _i32p, _i32p, _u8p, _f32p] + [C.c_int] * 5
     L.uep_oracle_dense_reroute_forward_rr.argtypes = [_u8p, _f32p, _i32p, _i32p, _u8p, _f32p] + [C.c_int] * 4
     L.uep_oracle_sparse_reroute32.argtypes = [_i32p, _i32p, C.c_int64, C.c_int, _i32p, _i32p, _i32p, C.c_int, C.c_int]
@@ -129,6 +130,19 @@ def init_master_placement(num_ranks: int, M: int, R: int, D: int | None = None) 
     p = Plan(*(np.empty(s, np.int32) for s in [(P,), (L, D), (L,), (L, D), (L, D), (L, D)]))
     lib().uep_oracle_init_master_placement(p.p2l, p.l2p, p.lcnts, p.quota, p.quota_prefix, p.rank_quota_prefix,
                                            num_ranks, M, R, D)
+    return p
+
+
+def legacy_solve_placement(global_loads: np.ndarray, num_ranks: int, M: int, R: int, nvl_ranks: int | None = None,
+                           balance_threshold: float = 1.0, D: int | None = None) -> Plan:
+    """The plan of legacy_placement=True (host-side solver of the reference): p2l, l2p, lcnts; quotas stay zero."""
+    loads = np.ascontiguousarray(global_loads, dtype=np.int32)
+    L, P = num_ranks * M, num_ranks * (M + R)
+    assert loads.shape == (L,)
+    D = D or num_ranks
+    p = Plan(*(np.zeros(s, np.int32) for s in [(P,), (L, D), (L,), (L, D), (L, D), (L, D)]))
+    lib().uep_oracle_legacy_solve_placement(loads, p.p2l, p.l2p, p.lcnts, num_ranks, M, R, nvl_ranks or num_ranks, D,
+                                            balance_threshold)
     return p
 
 

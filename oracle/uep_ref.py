@@ -175,3 +175,32 @@ class Workspace:
         if self.handle:
             lib().uep_ref_workspace_destroy(self.handle)
             self.handle = None
+
+
+# ---- the reference's legacy host-side solver (no GPU needed) ---------------------------------
+LEGACY_SO = os.path.join(_HERE, "_ref", "libuep_ref_legacy.so")
+_legacy = None
+
+
+def legacy_available() -> bool:
+    return os.path.exists(LEGACY_SO)
+
+
+def legacy_solve_host(global_loads, num_ranks: int, M: int, R: int, nvl_ranks: int, balance_threshold: float = 1.0,
+                      D: int | None = None):
+    """(p2l, l2p, lcnts) as csrc/kernels/legacy/placement_cpu.cpp computes them, on host arrays."""
+    import numpy as np
+
+    global _legacy
+    if _legacy is None:
+        _legacy = C.CDLL(LEGACY_SO)
+        _legacy.uep_ref_legacy_solve_host.argtypes = [_vp] * 4 + [_i] * 6 + [_f]
+    loads = np.ascontiguousarray(global_loads, dtype=np.int32)
+    L, P = num_ranks * M, num_ranks * (M + R)
+    D = D or num_ranks
+    p2l = np.zeros(P, np.int32)
+    l2p = np.zeros((L, D), np.int32)
+    lcnts = np.zeros(L, np.int32)
+    _legacy.uep_ref_legacy_solve_host(loads.ctypes.data, p2l.ctypes.data, l2p.ctypes.data, lcnts.ctypes.data, L, num_ranks,
+                                      M, R, nvl_ranks, D, balance_threshold)
+    return p2l, l2p, lcnts

@@ -224,3 +224,38 @@ def reroute_inputs(rc: RerouteCase):
     keys = np.log(p)[None, :] + rng.gumbel(size=(T, L))
     part = np.argpartition(-keys, K - 1, axis=1)[:, :K] if K < L else np.tile(np.arange(L), (T, 1))
     return part.astype(np.int32)
+
+
+def legacy_cases():
+    """Load vectors for the legacy (host-side) placement solver: dicts with name, loads [L], N, M, R, nvl,
+    balance_threshold. Covers: no redundancy, one-rank domains, thresholds that stop the granting early,
+    ties between experts and between ranks, all-zero loads, more slots than useful instances, several domains."""
+    out = []
+
+    def add(name, loads, N, M, R, nvl, bt):
+        out.append(dict(name=name, loads=np.ascontiguousarray(loads, np.int32), N=N, M=M, R=R, nvl=nvl, balance_threshold=bt))
+
+    for i, (N, M, R, T, K, s, seed) in enumerate([(8, 8, 2, 4096, 8, 1.2, 33), (8, 16, 4, 8192, 8, 1.3, 34),
+                                                   (8, 32, 8, 16384, 8, 1.5, 35), (4, 4, 1, 512, 2, 1.1, 36),
+                                                   (2, 8, 3, 1024, 4, 2.0, 37), (16, 4, 2, 2048, 4, 1.4, 38)]):
+        lpr = _zipf_loads(N, M, T, K, s, seed)
+        for bt in (1.0, 1.25, 2.0):
+            add(f"zipf{i}_bt{bt}", lpr.sum(0), N, M, R, N, bt)
+    lpr = _zipf_loads(8, 8, 4096, 8, 1.3, 41)
+    add("two_domains", lpr.sum(0), 8, 8, 2, 4, 1.0)
+    add("one_rank_domains", lpr.sum(0), 8, 8, 2, 1, 1.0)
+    add("no_redundant", lpr.sum(0), 8, 8, 0, 8, 1.0)
+    add("all_zero", np.zeros(64, np.int32), 8, 8, 2, 8, 1.0)
+    add("all_equal", np.full(64, 1000, np.int32), 8, 8, 2, 8, 1.0)
+    add("all_equal_bt", np.full(64, 1000, np.int32), 8, 8, 2, 8, 1.5)
+    one_hot = np.zeros(32, np.int32)
+    one_hot[5] = 100000
+    add("one_hot_many_slots", one_hot, 4, 8, 6, 4, 1.0)  # an expert gets at most G-1 extra instances
+    rng = np.random.Generator(np.random.PCG64(77))
+    for i in range(12):
+        N = int(rng.choice([2, 4, 8]))
+        M = int(rng.integers(1, 9))
+        R = int(rng.integers(1, 5))
+        loads = rng.integers(0, 50, N * M).astype(np.int32) * int(rng.choice([1, 1, 100]))  # small values: many ties
+        add(f"random{i}", loads, N, M, R, N, float(rng.choice([1.0, 1.1, 3.0])))
+    return out

@@ -78,3 +78,26 @@ def test_reroute_against_recorded_reference(golden):
         dense_from_sparse = np.zeros((T, P), np.bool_)
         dense_from_sparse[np.arange(T)[:, None], sparse] = True
         assert np.array_equal(dense_from_sparse, out_map), name
+
+
+def test_oracle_legacy_solver_matches_reference_golden():
+    """The restatement of the reference's legacy host-side solver against what that solver itself produced
+    (tests/golden/ref_legacy_golden.npz, written by tests/golden/make_legacy_golden.py), and live when the
+    in-place build of it is present."""
+    import cases as Cs
+    from oracle import uep_ref
+
+    golden = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_legacy_golden.npz"))
+    cases = Cs.legacy_cases()
+    assert sorted(golden["names"].tolist()) == sorted(c["name"] for c in cases)
+    replicated = 0
+    for c in cases:
+        plan = O.legacy_solve_placement(c["loads"], c["N"], c["M"], c["R"], c["nvl"], c["balance_threshold"])
+        for f in ("p2l", "l2p", "lcnts"):
+            assert np.array_equal(getattr(plan, f), golden[f"{c['name']}/{f}"]), (c["name"], f)
+        assert not plan.quota.any() and not plan.rank_quota_prefix.any()
+        replicated += int((plan.lcnts > 1).sum())
+        if uep_ref.legacy_available():
+            p2l, l2p, lcnts = uep_ref.legacy_solve_host(c["loads"], c["N"], c["M"], c["R"], c["nvl"], c["balance_threshold"])
+            assert np.array_equal(p2l, plan.p2l) and np.array_equal(l2p, plan.l2p) and np.array_equal(lcnts, plan.lcnts)
+    assert replicated > 50

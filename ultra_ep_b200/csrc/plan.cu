@@ -77,17 +77,60 @@ __device__ void histogram_slice(int input_kind, const void* input, int T, int K_
         }
     } else {
         const int64_t n = static_cast<int64_t>(T) * K_or_L;
-        const int64_t per = (n + nparts - 1) / nparts;
+        // slices start at multiples of four entries so that aligned inputs can be read 16 bytes at a time;
+        // a thread issues all of its vector loads before it touches the first result
+        const int64_t per = ((n + nparts - 1) / nparts + 3) & ~static_cast<int64_t>(3);
         const int64_t begin = min(static_cast<int64_t>(part) * per, n), end = min(begin + per, n);
         if (input_kind == 1) {
             const int32_t* ids = static_cast<const int32_t*>(input);
-            for (int64_t i = begin + tid; i < end; i += nthreads) {
+            int64_t i0 = begin;
+            if ((reinterpret_cast<uintptr_t>(ids) & 15u) == 0) {
+                const int64_t nvec = (end - begin) / 4;
+                const int4* v = reinterpret_cast<const int4*>(ids + begin);
+                for (int64_t j0 = 0; j0 < nvec; j0 += 4 * nthreads) {
+                    int4 x[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int64_t j = j0 + tid + static_cast<int64_t>(u) * nthreads;
+                        x[u] = j < nvec ? __ldg(v + j) : make_int4(-1, -1, -1, -1);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int e[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            if (e[c] >= 0 && e[c] < L) atomicAdd(hist + e[c], 1);
+                        }
+                    }
+                }
+                i0 = begin + nvec * 4;
+            }
+            for (int64_t i = i0 + tid; i < end; i += nthreads) {
                 const int32_t e = ids[i];
                 if (e >= 0 && e < L) atomicAdd(hist + e, 1);
             }
         } else {
             const int64_t* ids = static_cast<const int64_t*>(input);
-            for (int64_t i = begin + tid; i < end; i += nthreads) {
+            int64_t i0 = begin;
+            if ((reinterpret_cast<uintptr_t>(ids) & 15u) == 0) {
+                const int64_t nvec = (end - begin) / 2;
+                const longlong2* v = reinterpret_cast<const longlong2*>(ids + begin);
+                for (int64_t j0 = 0; j0 < nvec; j0 += 4 * nthreads) {
+                    longlong2 x[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int64_t j = j0 + tid + static_cast<int64_t>(u) * nthreads;
+                        x[u] = j < nvec ? __ldg(v + j) : make_longlong2(-1, -1);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (x[u].x >= 0 && x[u].x < L) atomicAdd(hist + static_cast<int>(x[u].x), 1);
+                        if (x[u].y >= 0 && x[u].y < L) atomicAdd(hist + static_cast<int>(x[u].y), 1);
+                    }
+                }
+                i0 = begin + nvec * 2;
+            }
+            for (int64_t i = i0 + tid; i < end; i += nthreads) {
                 const int64_t e = ids[i];
                 if (e >= 0 && e < L) atomicAdd(hist + static_cast<int>(e), 1);
             }
