@@ -86,6 +86,14 @@ int uep_solve_placement(const int32_t* loads_per_rank, int32_t* global_loads_out
                         int num_ranks, int nvl_ranks, int M, int R, int D, const uep_solver_params* params,
                         int my_rank, int32_t* status, void* stream);
 
+/* Plan of legacy_placement=True from the group's total loads [L]: p2l, l2p, lcnts; the quota tensors are zeroed
+ * (the reroute of this mode is round-robin). Replaces kernels::legacy::solve_placement
+ * (csrc/kernels/legacy/placement_cpu.cpp:17-241), which copies the loads to the host, synchronises the stream
+ * and solves there; this one is a kernel with the same arithmetic (doubles) and tie-breaks. */
+int uep_legacy_solve_placement(const int32_t* global_loads, int32_t* p2l, int32_t* l2p, int32_t* lcnts, int32_t* quota,
+                               int32_t* quota_prefix, int32_t* rank_quota_prefix, int num_ranks, int nvl_ranks, int M,
+                               int R, int D, float balance_threshold, int32_t* status, void* stream);
+
 /* Masters-only plan. Replaces kernels::init_master_placement (csrc/kernels/placement.cu:1504-1559). */
 int uep_init_master_placement(int32_t* p2l, int32_t* l2p, int32_t* lcnts, int32_t* quota, int32_t* quota_prefix,
                               int32_t* rank_quota_prefix, int num_ranks, int M, int R, int D, void* stream);
@@ -165,7 +173,7 @@ typedef struct uep_config {
     int64_t expert_fc1_weight_scale_numel, expert_fc2_weight_scale_numel;
     int32_t grad_element_bytes; /* must be 4 */
     int32_t is_train;
-    int32_t legacy_placement;   /* must be 0: the legacy CPU solver is outside the hot path */
+    int32_t legacy_placement;   /* 1: counts-only greedy plan (uep_legacy_solve_placement's rule) + round-robin reroute */
     uep_solver_params solver;
     int32_t quota_kernel_stage;         /* 0 or 1; both give identical plans, accepted for compatibility */
     int32_t grad_reduce_num_sms;        /* even, > 0, clamped to the SM count                */

@@ -415,3 +415,60 @@ def test_manager_argument_errors(native_lib, cuda_device):
     with pytest.raises(capi.UepError):
         group.update_placement(5, ids)
     group.destroy()
+
+
+def test_legacy_placement_mode(native_lib, cuda_device):
+    """legacy_placement=True through the manager: the counts-only greedy plan from the gathered loads, round-robin
+    reroute (dense and sparse) over an expert's instances, weights synced to every instance."""
+    cfg = W.CONFIGS["cfg1_plan_reroute"]
+    fc1, fc2 = 2 * 64 * 128, 64 * 128
+    mcfg = sim.make_config(cfg.ep, cfg.masters, cfg.redundant, 2, fc1_numel=fc1, fc2_numel=fc2, weight_elem_bytes=1,
+                           is_train=False, sim=True)
+    mcfg.legacy_placement = 1
+    group = sim.SimGroup(mcfg)
+    ids = [W.routing_ids(cfg, r) for r in range(cfg.ep)]
+    lpr = np.stack([np.bincount(x.reshape(-1), minlength=cfg.num_experts) for x in ids]).astype(np.int32)
+    plan = O.legacy_solve_placement(lpr.sum(0), cfg.ep, cfg.masters, cfg.redundant, cfg.ep, 1.0)
+    assert int((plan.lcnts > 1).sum()) > 0
+    d_ids = [torch.from_numpy(x).to(cuda_device) for x in ids]
+    group.update_placement(1, d_ids)
+    phys = group.reroute_sparse(1, d_ids)
+    maps = [W.ids_to_map(x, cfg.num_experts) for x in ids]
+    probs = [W.probs_for_map(m, 7 + r) for r, m in enumerate(maps)]
+    out_probs, out_maps = group.reroute_dense(1, [torch.from_numpy(m).to(cuda_device) for m in maps],
+                                              [torch.from_numpy(p).to(cuda_device) for p in probs])
+    shards = _master_tensors(cfg, group, [fc1, fc2])
+    tables = [group.pointer_tables(sh) for sh in shards]
+    for r in range(cfg.ep):
+        group.buffer(r, capi.BUF_REPLICA_WEIGHT).fill_(0xEE)
+    group.weight_sync(1, tables[0], tables[1])
+    torch.cuda.synchronize()
+    group.check_status()
+    D = cfg.ep
+    for r in range(cfg.ep):
+        got = group.plan(r, 1)
+        for f in ("p2l", "l2p", "lcnts"):
+            assert np.array_equal(got[f].cpu().numpy(), getattr(plan, f)), f"rank {r} field {f}"
+        assert not got["quota"].any() and not got["rank_quota_prefix"].any()
+        # round-robin: the n-th token (row-major) of expert e on this rank goes to instance n mod C
+        flat = ids[r].reshape(-1)
+        expect = np.empty_like(flat)
+        seen = np.zeros(cfg.num_experts, np.int64)
+        for i, e in enumerate(flat):
+            expect[i] = plan.l2p.reshape(-1, D)[e, seen[e] % plan.lcnts[e]]
+            seen[e] += 1
+        assert np.array_equal(phys[r].cpu().numpy().reshape(-1), expect), f"rank {r} sparse round-robin"
+        exp_map = np.zeros((ids[r].shape[0], group.P), bool)
+        exp_map[np.repeat(np.arange(ids[r].shape[0]), ids[r].shape[1]), expect] = True
+        assert np.array_equal(out_maps[r].cpu().numpy(), exp_map), f"rank {r} dense round-robin"
+        # every instance holds its expert's bytes
+        rep = group.buffer(r, capi.BUF_REPLICA_WEIGHT).cpu()
+        Lp = cfg.masters + cfg.redundant
+        for slot in range(cfg.redundant):
+            l = int(plan.p2l[r * Lp + cfg.masters + slot])
+            if l >= 0:
+                src = torch.cat([shards[0][l // cfg.masters][l % cfg.masters], shards[1][l // cfg.masters][l % cfg.masters]]).cpu()
+                assert torch.equal(rep[slot, :fc1 + fc2], src), f"rank {r} slot {slot}"
+            else:
+                assert bool((rep[slot] == 0xEE).all())
+    group.destroy()

@@ -132,3 +132,29 @@ def test_init_master_placement(native_lib, cuda_device):
     exp = O.init_master_placement(N, M, R)
     for b, f in zip(bufs, G.PLAN_FIELDS):
         assert np.array_equal(b.cpu().numpy(), getattr(exp, f)), f
+
+
+@pytest.mark.parametrize("case", Cs.legacy_cases(), ids=lambda c: c["name"])
+def test_legacy_solver_matches_oracle(native_lib, cuda_device, case):
+    """legacy_placement=True: the kernel against the restatement of the reference's host-side solver (which is
+    itself pinned to that solver's recorded outputs) — p2l, l2p, lcnts bit for bit, quotas zero."""
+    from ultra_ep_b200 import capi
+
+    N, M, R, nvl = case["N"], case["M"], case["R"], case["nvl"]
+    L, P, D = N * M, N * (M + R), N
+    plan = O.legacy_solve_placement(case["loads"], N, M, R, nvl, case["balance_threshold"])
+    loads = torch.from_numpy(case["loads"]).to(cuda_device)
+    out = {k: torch.full(shape, 7777, dtype=torch.int32, device=cuda_device)
+           for k, shape in [("p2l", (P,)), ("l2p", (L, D)), ("lcnts", (L,)), ("quota", (L, D)), ("quota_prefix", (L, D)),
+                            ("rank_quota_prefix", (L, D))]}
+    status = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    capi.check(capi.lib().uep_legacy_solve_placement(
+        loads.data_ptr(), out["p2l"].data_ptr(), out["l2p"].data_ptr(), out["lcnts"].data_ptr(), out["quota"].data_ptr(),
+        out["quota_prefix"].data_ptr(), out["rank_quota_prefix"].data_ptr(), N, nvl, M, R, D, case["balance_threshold"],
+        status.data_ptr(), G.stream_ptr()), "uep_legacy_solve_placement")
+    torch.cuda.synchronize()
+    assert status.cpu().tolist() == [0, 0]
+    for f in ("p2l", "l2p", "lcnts"):
+        assert np.array_equal(out[f].cpu().numpy(), getattr(plan, f)), (case["name"], f)
+    for f in ("quota", "quota_prefix", "rank_quota_prefix"):
+        assert not out[f].any()

@@ -73,6 +73,7 @@ SIGNATURES = {
     "uep_histogram_ids64": (_i, [_vp, _i64, _i, _vp, _vp]),
     "uep_histogram_map": (_i, [_vp, _i, _i, _vp, _vp]),
     "uep_solve_placement": (_i, [_vp] * 8 + [_i] * 5 + [C.POINTER(SolverParams), _i, _vp, _vp]),
+    "uep_legacy_solve_placement": (_i, [_vp] * 7 + [_i] * 5 + [C.c_float, _vp, _vp]),
     "uep_init_master_placement": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "uep_reroute_scratch_elems": (_i64, [_i64, _i, _i]),
     "uep_dense_reroute_forward": (_i, [_vp] * 8 + [_i] * 6 + [_vp]),

@@ -66,6 +66,7 @@ struct PlanCall {
     uint64_t timeout_ns;
     int ctas_per_rank;
     int withhold_rank;  // test hook: this rank does not publish its flags (-1: none)
+    int legacy;         // 1: legacy placement solver (counts only; the reroute is then round-robin)
     unsigned long long* trace;  // optional: 8 globaltimer stamps per hosted rank (tuning aid), or null
 };
 cudaError_t launch_plan(const PlanCall& call, cudaStream_t stream);

@@ -228,7 +228,6 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
     if (cfg->grad_element_bytes != 4) return fail(UEP_ERR_INVALID, "manager_create: only fp32 gradients are supported");
     if (cfg->expert_fc1_numel < 0 || cfg->expert_fc2_numel < 0 || cfg->expert_fc1_weight_scale_numel < 0 || cfg->expert_fc2_weight_scale_numel < 0)
         return fail(UEP_ERR_INVALID, "manager_create: negative numel");
-    if (cfg->legacy_placement) return fail(UEP_ERR_UNSUPPORTED, "manager_create: legacy (host-side, round-robin) placement is outside this library");
     if (cfg->quota_kernel_stage != 0 && cfg->quota_kernel_stage != 1) return fail(UEP_ERR_INVALID, "manager_create: quota_kernel_stage supports only {0,1}");
     if (cfg->weight_sync_plan_mode < 0 || cfg->weight_sync_plan_mode > 2) return fail(UEP_ERR_INVALID, "manager_create: weight_sync_plan_mode must be 0, 1 or 2");
     if (cfg->weight_sync_relay_min_replicas < 0 || cfg->weight_sync_relay_max_relays < 1 || cfg->weight_sync_relay_min_fanout_gain < 0)
@@ -489,6 +488,7 @@ int uep_update_placement(uep_manager* m, int layer_id, int input_kind, const voi
     call.timeout_ns = m->timeout_ns;
     call.ctas_per_rank = plan_ctas_per_rank(input_kind, max_T, K_or_L, m->nlocal, m->num_sms);
     call.withhold_rank = m->withhold_rank;
+    call.legacy = m->cfg.legacy_placement ? 1 : 0;
     call.trace = m->sync_trace ? m->sync_trace + 8 * 1000 : nullptr;  // the last rows of the trace buffer
     UEP_CUDA_TRY(launch_plan(call, stream));
     const int slot = plan_slot(m, layer_id);
@@ -608,7 +608,8 @@ int uep_reroute_dense_forward(uep_manager* m, int layer_id, const uint8_t* const
         b.a[i] = DenseFwdArgs{routing_maps[i], probs[i], p.l2p, p.lcnts, p.rank_quota_prefix, m->ranks[i].scratch,
                               expanded_maps[i], expanded_probs[i], T[i]};
     }
-    UEP_CUDA_TRY(launch_dense_forward(b, m->L, m->P, m->D, 1, m->cfg.solver.reroute_interleave, stream));
+    // legacy placement has no quotas: its reroute is round-robin over an expert's instances
+    UEP_CUDA_TRY(launch_dense_forward(b, m->L, m->P, m->D, m->cfg.legacy_placement ? 0 : 1, m->cfg.solver.reroute_interleave, stream));
     return UEP_OK;
 }
 
@@ -650,7 +651,7 @@ int uep_reroute_sparse(uep_manager* m, int layer_id, int ids_kind, const void* c
         const PlanPtrs p = plan_ptrs(m, m->ranks[i], layer_id);
         b.a[i] = SparseArgs{ids[i], out[i], p.l2p, p.lcnts, p.rank_quota_prefix, m->ranks[i].scratch, T[i]};
     }
-    UEP_CUDA_TRY(launch_sparse_reroute(b, ids_kind, K, m->L, m->D, m->cfg.solver.reroute_interleave, stream));
+    UEP_CUDA_TRY(launch_sparse_reroute(b, ids_kind, K, m->L, m->D, m->cfg.legacy_placement ? 2 : m->cfg.solver.reroute_interleave, stream));
     return UEP_OK;
 }
 

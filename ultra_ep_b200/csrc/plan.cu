@@ -21,6 +21,9 @@
 
 #include <atomic>
 
+#include <algorithm>
+#include <cstring>
+
 #include "internal.h"
 #include "solver.cuh"
 
@@ -307,6 +310,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     a.locality = call.params.locality_aware;
     a.eps = call.params.oracle_eps;
     a.my_rank = me;
+    a.legacy = call.legacy;
     a.trace = call.trace != nullptr ? call.trace + (kMaxLocalRanks + local) * 8 : nullptr;
     const int num_domains = N / call.G;
     for (int d = 0; d < num_domains; ++d) solve_domain_dispatch(a, d, smem_raw, rk.status);
@@ -314,7 +318,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
 }
 
 size_t plan_smem_bytes(int N, int G, int M) {
-    const size_t solver = solver_smem_bytes(G * M, G);
+    const size_t solver = std::max(solver_smem_bytes(G * M, G), legacy_smem_bytes(G * M, G));
     const size_t hist = sizeof(int32_t) * static_cast<size_t>(N) * M;
     return (solver > hist ? solver : hist) + 16;
 }
@@ -422,12 +426,40 @@ int uep_solve_placement(const int32_t* loads_per_rank, int32_t* global_loads_out
     a.locality = params->locality_aware;
     a.eps = params->oracle_eps;
     a.my_rank = my_rank;
+    a.legacy = 0;
     a.trace = nullptr;
     const size_t smem = solver_smem_bytes(nvl_ranks * M, nvl_ranks) + 16;
     UEP_CUDA_TRY(ensure_smem(reinterpret_cast<const void*>(solve_kernel), smem));
     count_launch();
     solve_kernel<<<num_ranks / nvl_ranks, kPlanThreads, smem, stream>>>(a, global_loads_out, 1,
                                                                         reinterpret_cast<DeviceStatus*>(status));
+    UEP_CUDA_TRY(cudaGetLastError());
+    return UEP_OK;
+}
+
+int uep_legacy_solve_placement(const int32_t* global_loads, int32_t* p2l, int32_t* l2p, int32_t* lcnts, int32_t* quota,
+                               int32_t* quota_prefix, int32_t* rank_quota_prefix, int num_ranks, int nvl_ranks, int M,
+                               int R, int D, float balance_threshold, int32_t* status, void* stream_) {
+    if (global_loads == nullptr) return fail(UEP_ERR_INVALID, "legacy_solve_placement: null loads");
+    if (nvl_ranks <= 0 || num_ranks <= 0 || num_ranks % nvl_ranks != 0 || M <= 0 || R < 0 || D < 1)
+        return fail(UEP_ERR_INVALID, "legacy_solve_placement: bad group shape");
+    if (nvl_ranks * M > kMaxExpertsPerDomain || nvl_ranks > kMaxRanksPerDomain || nvl_ranks * R > kMaxExportsPerDomain)
+        return fail(UEP_ERR_INVALID, "legacy_solve_placement: domain exceeds the static limits (512 experts, 72 ranks, 512 replicas)");
+    if (D < (nvl_ranks < num_ranks ? nvl_ranks : num_ranks))
+        return fail(UEP_ERR_INVALID, "legacy_solve_placement: max_replicas_dim smaller than the NVLink domain");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    SolveArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.global_loads = global_loads;
+    a.p2l = p2l; a.l2p = l2p; a.lcnts = lcnts; a.quota = quota; a.quota_prefix = quota_prefix;
+    a.rank_quota_prefix = rank_quota_prefix;
+    a.N = num_ranks; a.G = nvl_ranks; a.M = M; a.R = R; a.D = D;
+    a.balance_threshold = balance_threshold;
+    a.legacy = 1;
+    const size_t smem = legacy_smem_bytes(nvl_ranks * M, nvl_ranks) + 16;
+    UEP_CUDA_TRY(ensure_smem(reinterpret_cast<const void*>(solve_kernel), smem));
+    count_launch();
+    solve_kernel<<<num_ranks / nvl_ranks, kPlanThreads, smem, stream>>>(a, nullptr, 0, reinterpret_cast<DeviceStatus*>(status));
     UEP_CUDA_TRY(cudaGetLastError());
     return UEP_OK;
 }

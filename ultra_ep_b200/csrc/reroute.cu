@@ -331,7 +331,7 @@ sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interlea
         int b = 0;
         for (int tl = 0; tl < tile; ++tl) b += tile_counts[static_cast<int64_t>(tl) * L + e];
         base[e] = b;
-        routers[e] = make_router(e, lcnts, rqp, D, true, interleave != 0);
+        routers[e] = make_router(e, lcnts, rqp, D, interleave != 2, interleave == 1);  // 2: round-robin (legacy placement)
     }
     __syncthreads();
     // ids may alias out: every entry is read and written by the same lane, the write comes
@@ -346,7 +346,7 @@ sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interlea
             out[i] = ids[i];
             return;
         }
-        const int j = replica_index(r, b, ordinal, rqp, D, true);
+        const int j = replica_index(r, b, ordinal, rqp, D, interleave != 2);
         out[i] = static_cast<IdT>(l2p[static_cast<int64_t>(b) * D + j]);
     });
 }

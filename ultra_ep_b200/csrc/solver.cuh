@@ -43,6 +43,7 @@ struct SolveArgs {
     int locality;
     float eps;
     int my_rank;
+    int legacy;  // 1: legacy placement (counts-only greedy, round-robin reroute) instead of the quota solver
     unsigned long long* trace;  // optional: 8 globaltimer stamps of the solver phases (tuning aid), or null
 };
 
@@ -725,7 +726,202 @@ __device__ void solve_domain(const SolveArgs& a, int domain, char* smem_raw, Dev
     stamp(5);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Legacy placement (legacy_placement=True). The reference solves this mode on the host after copying the
+// loads back and synchronising the stream (csrc/kernels/legacy/placement_cpu.cpp:17-241); here it is one
+// warp of the plan kernel, so the mode costs no host round trip. Same greedy, same doubles (IEEE
+// division and addition, never contracted), same tie-breaks:
+//   1. redundant slots are granted one at a time to the expert with the largest load per instance
+//      (ties: lower id; at most G-1 extra instances per expert; with balance_threshold > 1 the granting
+//      stops once the best load per instance is within threshold x the mean load per master slot);
+//   2. the extra instances, ordered by load per instance descending then expert id, go to the rank
+//      with the smallest accumulated load (ties: lower rank) that has a free slot and does not hold
+//      the expert; an instance that finds no rank is dropped.
+// Quotas are not used in this mode: the reroute is round-robin over an expert's instances.
+// Shared memory: legacy_smem_bytes(E, G). All threads of the CTA must call it.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline size_t legacy_smem_bytes(int E, int G) {
+    return sizeof(double) * (static_cast<size_t>(E) + 2 * kMaxExportsPerDomain + solver_gpad(G)) +
+           sizeof(int32_t) * (3 * static_cast<size_t>(E) + 2 * kMaxExportsPerDomain + solver_gpad(G) + 8) +
+           sizeof(uint32_t) * static_cast<size_t>(E) * solver_ns(G);
+}
+
+__device__ inline void legacy_solve_domain(const SolveArgs& a, int domain, char* smem_raw, DeviceStatus* status) {
+    const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.G, M = a.M, R = a.R, D = a.D, E = G * M, Lp = M + R, ns = solver_ns(G);
+    const int rank0 = domain * G, log0 = rank0 * M;
+    double* score = reinterpret_cast<double*>(smem_raw);        // [E] load per instance
+    double* xkey = score + E;                                    // [512] extras: load per instance
+    double* xkey_sorted = xkey + kMaxExportsPerDomain;           // [512]
+    double* rank_load = xkey_sorted + kMaxExportsPerDomain;      // [Gpad]
+    int32_t* loads = reinterpret_cast<int32_t*>(rank_load + solver_gpad(G));  // [E]
+    int32_t* cnt = loads + E;                                    // [E] instances
+    int32_t* placed = cnt + E;                                   // [E] instances placed so far (incl. master)
+    int32_t* xid = placed + E;                                   // [512] extras: expert
+    int32_t* xid_sorted = xid + kMaxExportsPerDomain;            // [512]
+    int32_t* used = xid_sorted + kMaxExportsPerDomain;           // [Gpad] redundant slots used per rank
+    int32_t* ctl = used + solver_gpad(G);                        // [8]
+    uint32_t* holds = reinterpret_cast<uint32_t*>(ctl + 8);      // [E][ns] ranks that hold the expert
+
+    for (int i = tid; i < G * Lp; i += nthreads) {
+        a.p2l[rank0 * Lp + i] = -1;
+        if (a.physical_loads != nullptr) a.physical_loads[rank0 * Lp + i] = 0;
+    }
+    for (int i = tid; i < E * D; i += nthreads) {
+        const int64_t idx = static_cast<int64_t>(log0) * D + i;
+        a.l2p[idx] = -1;
+        a.quota[idx] = 0;
+        a.quota_prefix[idx] = 0;
+        a.rank_quota_prefix[idx] = 0;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += nthreads) {
+        const int l = log0 + e;
+        loads[e] = __ldcg(a.global_loads + l);
+        cnt[e] = 1;
+        placed[e] = 1;
+        score[e] = static_cast<double>(loads[e]);
+        const int phys = (rank0 + e / M) * Lp + e % M;
+        a.p2l[phys] = l;
+        a.l2p[static_cast<int64_t>(l) * D] = phys;
+        for (int w = 0; w < ns; ++w) holds[e * ns + w] = 0;
+        holds[e * ns + ((e / M) >> 5)] = 1u << ((e / M) & 31);
+    }
+    __syncthreads();
+    const bool search = R > 0 && G > 1;
+    if (warp == 0 && search) {
+        // 1. grant the slots
+        double total = 0.0;
+        for (int e = lane; e < E; e += kWarp) total = __dadd_rn(total, static_cast<double>(loads[e]));  // integers: exact in any order
+        for (int off = 16; off > 0; off >>= 1) total = __dadd_rn(total, __shfl_xor_sync(kFullMask, total, off));
+        const double mean_per_slot = total > 0.0 ? __ddiv_rn(total, static_cast<double>(G * M)) : 0.0;
+        const double stop_at = __dmul_rn(mean_per_slot, static_cast<double>(a.balance_threshold));
+        for (int slot = 0; slot < G * R; ++slot) {
+            double best = -1.0;
+            int best_e = -1;
+            for (int e = lane; e < E; e += kWarp) {
+                if (cnt[e] - 1 >= G - 1) continue;
+                if (score[e] > best) {  // ascending scan: equal scores keep the lower id
+                    best = score[e];
+                    best_e = e;
+                }
+            }
+            for (int off = 16; off > 0; off >>= 1) {
+                const double ob = __shfl_xor_sync(kFullMask, best, off);
+                const int oe = __shfl_xor_sync(kFullMask, best_e, off);
+                if (oe >= 0 && (best_e < 0 || ob > best || (ob == best && oe < best_e))) {
+                    best = ob;
+                    best_e = oe;
+                }
+            }
+            if (a.balance_threshold > 1.0f && mean_per_slot > 0.0 && best <= stop_at) break;
+            if (best_e < 0) break;
+            if (lane == 0) {
+                cnt[best_e] += 1;
+                score[best_e] = __ddiv_rn(static_cast<double>(loads[best_e]), static_cast<double>(cnt[best_e]));
+            }
+            __syncwarp();
+        }
+        // the extra instances, expert after expert
+        int n = 0;
+        for (int e0 = 0; e0 < E; e0 += kWarp) {
+            const int e = e0 + lane;
+            const int extra = e < E ? cnt[e] - 1 : 0;
+            int incl = extra;
+            for (int off = 1; off < kWarp; off <<= 1) {
+                const int t = __shfl_up_sync(kFullMask, incl, off);
+                if (lane >= off) incl += t;
+            }
+            for (int j = 0; j < extra; ++j) {
+                const int o = n + incl - extra + j;
+                if (o < kMaxExportsPerDomain) {
+                    xid[o] = e;
+                    xkey[o] = score[e];
+                }
+            }
+            n += __shfl_sync(kFullMask, incl, kWarp - 1);
+        }
+        if (lane == 0) ctl[0] = n < kMaxExportsPerDomain ? n : kMaxExportsPerDomain;
+    }
+    __syncthreads();
+    if (search) {
+        // order the extras: larger load per instance first, then the lower expert; instances of one expert are
+        // identical, their mutual order is their list order. Rank by counting, all threads.
+        const int n = ctl[0];
+        for (int i = tid; i < n; i += nthreads) {
+            const double k = xkey[i];
+            const int e = xid[i];
+            int pos = 0;
+            for (int j = 0; j < n; ++j) {
+                const double kj = xkey[j];
+                const int ej = xid[j];
+                pos += (kj > k || (kj == k && (ej < e || (ej == e && j < i)))) ? 1 : 0;
+            }
+            xkey_sorted[pos] = k;
+            xid_sorted[pos] = e;
+        }
+        for (int r = tid; r < G; r += nthreads) {
+            double sum = 0.0;
+            for (int m = 0; m < M; ++m) sum = __dadd_rn(sum, score[r * M + m]);  // load / instances, masters in order
+            rank_load[r] = sum;
+            used[r] = 0;
+        }
+    }
+    __syncthreads();
+    if (warp == 0 && search) {
+        // 2. place them
+        const int n = ctl[0];
+        for (int i = 0; i < n; ++i) {
+            const int e = xid_sorted[i];
+            double best = 0.0;
+            int target = -1;
+            for (int r = lane; r < G; r += kWarp) {
+                if (used[r] >= R || ((holds[e * ns + (r >> 5)] >> (r & 31)) & 1u)) continue;
+                if (target < 0 || rank_load[r] < best) {  // ascending scan: equal loads keep the lower rank
+                    best = rank_load[r];
+                    target = r;
+                }
+            }
+            for (int off = 16; off > 0; off >>= 1) {
+                const double ob = __shfl_xor_sync(kFullMask, best, off);
+                const int ot = __shfl_xor_sync(kFullMask, target, off);
+                if (ot >= 0 && (target < 0 || ob < best || (ob == best && ot < target))) {
+                    best = ob;
+                    target = ot;
+                }
+            }
+            if (lane == 0) {
+                if (target < 0) {
+                    cnt[e] -= 1;
+                } else {
+                    const int l = log0 + e;
+                    const int phys = (rank0 + target) * Lp + M + used[target];
+                    const int slot = placed[e];
+                    if (slot < D) {
+                        a.p2l[phys] = l;
+                        a.l2p[static_cast<int64_t>(l) * D + slot] = phys;
+                    } else {
+                        report_error(status, UEP_DEV_BAD_PLAN, l);
+                    }
+                    placed[e] = slot + 1;
+                    rank_load[target] = __dadd_rn(rank_load[target], xkey_sorted[i]);
+                    used[target] += 1;
+                    holds[e * ns + (target >> 5)] |= 1u << (target & 31);
+                }
+            }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += nthreads) a.lcnts[log0 + e] = cnt[e];
+    __syncthreads();
+}
+
 __device__ inline void solve_domain_dispatch(const SolveArgs& a, int domain, char* smem_raw, DeviceStatus* status) {
+    if (a.legacy) {
+        legacy_solve_domain(a, domain, smem_raw, status);
+        return;
+    }
     const int ns = solver_ns(a.G);
     if (ns == 1) solve_domain<1>(a, domain, smem_raw, status);
     else if (ns == 2) solve_domain<2>(a, domain, smem_raw, status);

@@ -337,7 +337,6 @@ solve_placement_for_test(torch::Tensor expert_loads, torch::Tensor expert_loads_
     UEP_ASSERT(num_ranks > 0 && num_nvl_ranks > 0 && num_ranks % num_nvl_ranks == 0);
     UEP_ASSERT(num_local_master_experts > 0 && num_local_redundant_experts >= 0);
     UEP_ASSERT(kernel_stage == 0 || kernel_stage == 1);
-    if (legacy_placement) throw std::runtime_error("legacy placement is outside this library");
     const int L = static_cast<int>(expert_loads.size(0));
     UEP_ASSERT(L == num_ranks * num_local_master_experts);
     UEP_ASSERT(expert_loads_per_rank.defined() && expert_loads_per_rank.is_cuda() &&
@@ -355,6 +354,15 @@ solve_placement_for_test(torch::Tensor expert_loads, torch::Tensor expert_loads_
     auto lpr = expert_loads_per_rank.contiguous();
     uep_solver_params prm{balance_threshold, locality_aware, min_tokens_per_replica, allow_zero_master_quota, oracle_eps, 1};
     const int src = rank_quota_source_rank >= 0 ? rank_quota_source_rank : (g_rt.initialized ? g_rt.rank : 0);
+    if (legacy_placement) {  // counts-only greedy plan from the total loads; quotas zero (csrc/ultra_ep.hpp:480-505 of the reference)
+        auto loads = expert_loads.contiguous();
+        check(uep_legacy_solve_placement(loads.data_ptr<int32_t>(), p2l.data_ptr<int32_t>(), l2p.data_ptr<int32_t>(),
+                                         lcnts.data_ptr<int32_t>(), quota.data_ptr<int32_t>(),
+                                         quota_prefix.data_ptr<int32_t>(), rqp.data_ptr<int32_t>(), num_ranks,
+                                         num_nvl_ranks, num_local_master_experts, num_local_redundant_experts, num_ranks,
+                                         balance_threshold, nullptr, current_stream()), "solve_placement_for_test");
+        return std::make_tuple(p2l, l2p, lcnts, quota, quota_prefix, rqp);
+    }
     check(uep_solve_placement(lpr.data_ptr<int32_t>(), loads_sum.data_ptr<int32_t>(), p2l.data_ptr<int32_t>(),
                               l2p.data_ptr<int32_t>(), lcnts.data_ptr<int32_t>(), quota.data_ptr<int32_t>(),
                               quota_prefix.data_ptr<int32_t>(), rqp.data_ptr<int32_t>(), num_ranks, num_nvl_ranks,

@@ -4,7 +4,8 @@ Drop-in for the reference's ultra_ep.Manager (ultra_ep/manager.py:18-770 of the 
 constructor arguments, methods, properties, buffer attributes and virtual-layer arithmetic.
 Differences: the expert-load trace (ULTRA_EP_LOAD_PROFILING) is recorded when the plan is made,
 from the per-slot loads the plan kernel writes itself, instead of by a separate kernel at reroute
-time (same trace files); its viewer is not part of this library; legacy_placement=True is refused.
+time (same trace files); its viewer is not part of this library; legacy_placement=True runs its counts-only greedy
+solver as a kernel (same results as the reference's host-side solver, no host round trip).
 """
 
 from __future__ import annotations
@@ -42,8 +43,9 @@ class Manager:
         expert_fc2_weight_scale_numel: int = 0,
         grad_dtype: torch.dtype = torch.float32,
     ):
-        if legacy_placement:
-            raise ValueError("legacy_placement=True (host-side solver, round-robin reroute) is not provided by this library")
+        if legacy_placement and load_profile_config().enabled:
+            raise AssertionError("UltraEP load profiling is only supported by quota placement; "
+                                 "disable ULTRA_EP_LOAD_PROFILING or legacy_placement.")
         _C = load()
         self.nvl_domain_size = init_runtime(group)
         self.group = group
@@ -108,7 +110,7 @@ class Manager:
         self.weight_sync_relay_min_replicas = tuning.weight_sync_relay_min_replicas
         self.weight_sync_relay_max_relays = tuning.weight_sync_relay_max_relays
         self.weight_sync_relay_min_fanout_gain = tuning.weight_sync_relay_min_fanout_gain
-        self.reroute_mode = "quota"
+        self.reroute_mode = "round_robin" if legacy_placement else "quota"
         self.runtime = _C.Manager(
             self.num_alloc_layers, num_local_master_experts, num_local_redundant_experts, expert_fc1_numel,
             expert_fc2_numel, self.weight_data_element_bytes, self.weight_scale_element_bytes,
