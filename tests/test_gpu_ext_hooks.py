@@ -75,6 +75,21 @@ def test_hook_argument_errors(C_ext, cuda_device):
     with pytest.raises(RuntimeError):
         C_ext.solve_placement_for_test(loads.cpu(), lpr, 4, 4, 1, 4)  # host tensor
     with pytest.raises(RuntimeError):
-        C_ext.solve_placement_for_test(loads, lpr, 4, 4, 1, 4, True)  # legacy placement
-    with pytest.raises(RuntimeError):
         C_ext.Manager(1, 2, 1, 16, 16, 2, 1, 0, 0, 4, True, True)     # runtime not initialised
+
+
+def test_solve_placement_for_test_hook_legacy(C_ext, cuda_device):
+    """legacy_placement=True through the hook: the counts-only greedy plan, quotas zero."""
+    for case in Cs.legacy_cases()[:9]:
+        if case["nvl"] != case["N"]:
+            continue
+        N, M, R = case["N"], case["M"], case["R"]
+        loads = torch.from_numpy(case["loads"]).to(cuda_device)
+        lpr = torch.zeros(N, N * M, dtype=torch.int32, device=cuda_device)
+        lpr[0] = loads
+        p2l, l2p, lcnts, quota, qp, rqp = C_ext.solve_placement_for_test(loads, lpr, N, M, R, N, True,
+                                                                         case["balance_threshold"])
+        plan = O.legacy_solve_placement(case["loads"], N, M, R, N, case["balance_threshold"])
+        assert np.array_equal(p2l.cpu().numpy(), plan.p2l) and np.array_equal(l2p.cpu().numpy(), plan.l2p)
+        assert np.array_equal(lcnts.cpu().numpy(), plan.lcnts)
+        assert not quota.any() and not qp.any() and not rqp.any()

@@ -404,7 +404,7 @@ def test_manager_argument_errors(native_lib, cuda_device):
     bad = sim.make_config(8, 8, 2, sim=True, fc1_numel=7, weight_elem_bytes=2)
     assert lib.uep_manager_create(C.byref(bad), C.byref(h)) == -1 and b"multiples of 16" in lib.uep_last_error()
     bad = sim.make_config(8, 8, 2, sim=True)
-    bad.legacy_placement = 1
+    bad.nvl_ranks = 4  # a group that spans two NVLink domains: the load exchange needs peer memory
     assert lib.uep_manager_create(C.byref(bad), C.byref(h)) == -4
     group = sim.SimGroup(sim.make_config(4, 2, 1, 2, sim=True, is_train=False))
     p, nd = C.c_void_p(), C.c_int()

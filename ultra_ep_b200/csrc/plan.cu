@@ -44,7 +44,8 @@ __device__ __forceinline__ void hist_add_swar(uint32_t word, int32_t* hist, int 
 
 // Count this CTA's slice of the input into hist[L] (shared memory, zeroed by the caller).
 // part / nparts split the rows (dense) or the entries (sparse) evenly.
-__device__ void histogram_slice(int input_kind, const void* input, int T, int K_or_L, int L, int part, int nparts,
+// (not inlined: its vector-load registers must not add to the solver's register pressure in plan_kernel)
+__device__ __noinline__ void histogram_slice(int input_kind, const void* input, int T, int K_or_L, int L, int part, int nparts,
                                 int32_t* hist) {
     const int tid = threadIdx.x, nthreads = blockDim.x;
     if (input_kind == 0) {

@@ -746,7 +746,7 @@ __host__ __device__ inline size_t legacy_smem_bytes(int E, int G) {
            sizeof(uint32_t) * static_cast<size_t>(E) * solver_ns(G);
 }
 
-__device__ inline void legacy_solve_domain(const SolveArgs& a, int domain, char* smem_raw, DeviceStatus* status) {
+__device__ __noinline__ void legacy_solve_domain(const SolveArgs& a, int domain, char* smem_raw, DeviceStatus* status) {
     const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31, warp = tid >> 5;
     const int G = a.G, M = a.M, R = a.R, D = a.D, E = G * M, Lp = M + R, ns = solver_ns(G);
     const int rank0 = domain * G, log0 = rank0 * M;
