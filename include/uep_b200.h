@@ -287,7 +287,7 @@ int uep_poll_status(uep_manager* m, int local_rank, int* code, int* detail);
 int uep_clear_status(uep_manager* m);
 
 /* Failure-detection test hook, host side only: from the next call on, the hosted rank `rank`
- * completes its work but does not publish its exchange / completion flags, so the ranks
+ * completes its work but does not publish its load row / completion flags, so the ranks
  * that wait for it run into their time limit and report UEP_DEV_TIMEOUT_*; -1 switches the
  * hook off. No device fault is involved. No counterpart in the reference (its waits are
  * unbounded, csrc/kernels/weight_sync.cu:666-677, csrc/kernels/ptx.cuh:73-86). */
@@ -295,9 +295,13 @@ int uep_debug_withhold_rank(uep_manager* m, int rank);
 
 /* Tuning aid: with UEP_SYNC_TRACE=1 in the environment when the manager is created, the
  * weight_sync kernel records eight %globaltimer stamps per CTA (start, set-up done, copies
- * issued, copies complete, fenced, ticket taken, flags done, unused); this copies the stamps of
- * the first max_ctas CTAs of the latest launch to host memory [max_ctas][8]. No counterpart in
- * the reference. */
+ * issued, copies complete, fenced, ticket taken, completion flags received, completion flags
+ * sent; the last two only in the CTA that finishes last); this copies the stamps of the first
+ * max_ctas CTAs of the latest launch to host memory [max_ctas][8]. Rows 1000.. and 1008.. of the
+ * same buffer hold, per hosted rank, the plan kernel's phases (histogram done, row published, rows
+ * gathered and reduced, -, solved, CTA start) and the solver's (enter, loads staged, sorted,
+ * searched, emitted, split). The withhold hook also makes a withheld rank skip publishing its
+ * load row. No counterpart in the reference. */
 int uep_debug_sync_trace(uep_manager* m, unsigned long long* host_out, int max_ctas);
 
 /* Counters for benchmarks: kernels launched by this library since the last reset. */
