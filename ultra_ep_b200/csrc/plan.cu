@@ -243,7 +243,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     //    a flag: one NVLink crossing, and the reader knows a word is this layer's when it sees it.
     const uint64_t epoch = s_epoch;
     const int slot = static_cast<int>(epoch & 1ull);
-    const uint32_t tag = static_cast<uint32_t>(epoch);
+    // never zero (the buffers start zeroed), period 2^32 - 1: an odd period, so the word that carried the same
+    // tag one period ago sat in the other parity slot and cannot be mistaken for this epoch's
+    const uint32_t tag = static_cast<uint32_t>(epoch % 0xFFFFFFFFull) + 1u;
     const int me = rk.my_rank;
     for (int i = tid; i < L; i += blockDim.x) {
         hist[i] = __ldcg(rk.local_hist + i);
