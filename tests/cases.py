@@ -199,6 +199,7 @@ def reroute_cases(full: bool = True):
         RerouteCase("rr_cfg3_r6", sc["cfg3_qwen3_235b_fp8"], 6, 8192, 8, 16),
         RerouteCase("rr_hot_min1", sc["one_hot_expert_min1"], 1, 700, 2, 17),
         RerouteCase("rr_locality_mix", sc["locality_mix"], 0, 512, 1, 18),
+        RerouteCase("rr_odd_L15", sc["skew9_N3_M5_R2"], 2, 333, 3, 21),  # L not a multiple of 4: scalar row paths
     ]
     if full:
         cases.append(RerouteCase("rr_replicas_gt8", sc["replicas_gt8"], 9, 2500, 2, 19))

@@ -182,6 +182,20 @@ dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_m
     }
 }
 
+__device__ __forceinline__ float routed_grad(const float* __restrict__ grad_expanded, const uint8_t* __restrict__ expanded_map,
+                                             const int32_t* __restrict__ l2p, const int32_t* __restrict__ lcnts, int64_t t,
+                                             int l, int P, int D) {
+    const int C = lcnts[l];
+    for (int r = 0; r < C; ++r) {
+        const int phys = l2p[static_cast<int64_t>(l) * D + r];
+        if (expanded_map[t * P + phys]) return grad_expanded[t * P + phys];
+    }
+    return 0.f;
+}
+
+// One thread per four logical experts of a token when the rows allow it (L a multiple of 4, map rows 4-byte and
+// gradient rows 16-byte aligned): the routing map is read a word at a time and the gradients leave as float4.
+// Most entries are not routed, so the kernel is a zero fill plus a few gathers.
 __global__ void __launch_bounds__(kRerouteThreads) dense_backward_kernel(Batch<DenseBwdArgs> batch, int L, int P, int D) {
     const DenseBwdArgs& a = batch.a[blockIdx.y];
     const float* __restrict__ grad_expanded = a.grad_expanded;
@@ -191,21 +205,30 @@ __global__ void __launch_bounds__(kRerouteThreads) dense_backward_kernel(Batch<D
     const int32_t* __restrict__ lcnts = a.lcnts;
     float* __restrict__ grad_probs = a.grad_probs;
     const int64_t total = static_cast<int64_t>(a.T) * L;
-    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        float g = 0.f;
-        if (map[idx]) {
-            const int64_t t = idx / L;
-            const int l = static_cast<int>(idx % L);
-            const int C = lcnts[l];
-            for (int r = 0; r < C; ++r) {
-                const int phys = l2p[static_cast<int64_t>(l) * D + r];
-                if (expanded_map[t * P + phys]) {
-                    g = grad_expanded[t * P + phys];
-                    break;
-                }
+    const int64_t gtid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t gsize = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const bool vec = (L % 4 == 0) && ((reinterpret_cast<uintptr_t>(map) & 3u) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(grad_probs) & 15u) == 0);
+    if (vec) {
+        const int groups = L / 4;
+        for (int64_t q = gtid; q < total / 4; q += gsize) {
+            const uint32_t m = __ldg(reinterpret_cast<const uint32_t*>(map) + q);
+            float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m != 0) {
+                const int64_t t = q / groups;
+                const int l0 = static_cast<int>(q % groups) * 4;
+                if (m & 0x000000FFu) g.x = routed_grad(grad_expanded, expanded_map, l2p, lcnts, t, l0, P, D);
+                if (m & 0x0000FF00u) g.y = routed_grad(grad_expanded, expanded_map, l2p, lcnts, t, l0 + 1, P, D);
+                if (m & 0x00FF0000u) g.z = routed_grad(grad_expanded, expanded_map, l2p, lcnts, t, l0 + 2, P, D);
+                if (m & 0xFF000000u) g.w = routed_grad(grad_expanded, expanded_map, l2p, lcnts, t, l0 + 3, P, D);
             }
+            reinterpret_cast<float4*>(grad_probs)[q] = g;
         }
+        return;
+    }
+    for (int64_t idx = gtid; idx < total; idx += gsize) {
+        float g = 0.f;
+        if (map[idx]) g = routed_grad(grad_expanded, expanded_map, l2p, lcnts, idx / L, static_cast<int>(idx % L), P, D);
         grad_probs[idx] = g;
     }
 }
@@ -522,7 +545,7 @@ cudaError_t launch_dense_backward(const Batch<DenseBwdArgs>& b, int L, int P, in
     int max_T = 0;
     for (int i = 0; i < b.n; ++i) max_T = b.a[i].T > max_T ? b.a[i].T : max_T;
     if (max_T == 0) return cudaSuccess;
-    int64_t blocks = (static_cast<int64_t>(max_T) * L + kRerouteThreads - 1) / kRerouteThreads;
+    int64_t blocks = (static_cast<int64_t>(max_T) * L / 4 + kRerouteThreads - 1) / kRerouteThreads + 1;
     const int64_t cap = (148 * 16) / b.n > 1 ? (148 * 16) / b.n : 1;
     if (blocks > cap) blocks = cap;
     count_launch();
