@@ -580,6 +580,24 @@ def run_backward(args, world, rank, dev, peak_hbm, max_over_ranks_each):
     maps = [torch.from_numpy(W.ids_to_map(x.cpu().numpy(), L)).to(dev) for x in ids]
     probs = [torch.rand(m.shape, dtype=torch.float32, device=dev) * m for m in maps]
     ex_probs, ex_maps = group.reroute_dense(0, maps, probs)
+    fwd = []
+    for it in range(3 + reps):
+        barrier()
+        flush_l2()
+        a, b = event_ms(torch, lambda: group.reroute_dense(0, maps, probs, out=(ex_probs, ex_maps)))
+        barrier()
+        if it >= 3:
+            fwd.append(a.elapsed_time(b))
+    fwd = max_over_ranks_each(fwd)
+    fwd_ms = sum(fwd) / len(fwd)
+    T_ = cfg.tokens_per_rank
+    fwd_bytes = len(ranks) * T_ * (L * 5 + P * 5)  # bool map + fp32 probs in, bool map + fp32 probs out (written once)
+    out["dense_reroute_forward_us"] = round(fwd_ms * 1e3, 1)
+    out["dense_reroute_forward_roofline"] = {"bound": "hbm", "achieved": round(fwd_bytes / 1e9 / (fwd_ms / 1e3), 1),
+                                             "peak": peak_hbm, "unit": "GB/s",
+                                             "frac": round(fwd_bytes / 1e9 / (fwd_ms / 1e3) / peak_hbm, 4),
+                                             "algorithmic_bytes_per_launch": fwd_bytes,
+                                             "note": "two launches (tile counts, scatter) into preallocated outputs"}
     grads = [torch.rand_like(p_) for p_ in ex_probs]
     bwd = []
     for it in range(3 + reps):

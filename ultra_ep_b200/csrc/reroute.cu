@@ -79,16 +79,37 @@ __device__ __forceinline__ int replica_index(const Router& r, int e, int ordinal
 }
 
 // ----------------------------------------------------------------------------- dense
+// Copies rows [r0, r1) of the bool map into shared memory, 16 bytes per thread when the tile starts on a
+// 16-byte boundary. The per-expert walks below then run over shared memory: walking a column of the map in
+// global memory costs one dependent memory round trip per row.
+__device__ __forceinline__ void stage_map_tile(const uint8_t* __restrict__ map, int r0, int r1, int L, uint8_t* smap) {
+    const int64_t first = static_cast<int64_t>(r0) * L;
+    const int bytes = (r1 - r0) * L;
+    const uint8_t* src = map + first;
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+        const int nvec = bytes / 16;
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            reinterpret_cast<uint4*>(smap)[i] = ld_global_nc_v4(src + static_cast<int64_t>(i) * 16);
+        }
+        done = nvec * 16;
+    }
+    for (int i = done + threadIdx.x; i < bytes; i += blockDim.x) smap[i] = src[i];
+}
+
 __global__ void __launch_bounds__(kRerouteThreads) dense_count_kernel(Batch<DenseFwdArgs> batch, int L) {
+    extern __shared__ __align__(128) char smem_raw[];  // [kDenseTileRows][L] bytes
     const DenseFwdArgs& a = batch.a[blockIdx.y];
-    const uint8_t* __restrict__ map = a.map;
     const int T = a.T;
     const int tile = blockIdx.x;
     const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
     if (r0 >= T) return;
+    uint8_t* smap = reinterpret_cast<uint8_t*>(smem_raw);
+    stage_map_tile(a.map, r0, r1, L, smap);
+    __syncthreads();
     for (int e = threadIdx.x; e < L; e += blockDim.x) {
         int c = 0;
-        for (int t = r0; t < r1; ++t) c += map[static_cast<int64_t>(t) * L + e] ? 1 : 0;
+        for (int t = 0; t < r1 - r0; ++t) c += smap[t * L + e] ? 1 : 0;
         a.scratch[static_cast<int64_t>(tile) * L + e] = c;
     }
 }
@@ -111,13 +132,14 @@ dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_m
     extern __shared__ __align__(128) char smem_raw[];
     // layout: inv[P] int32 | choice[rows][L] uint8
     int32_t* inv = reinterpret_cast<int32_t*>(smem_raw);
-    uint8_t* choice = reinterpret_cast<uint8_t*>(inv + P);
+    uint8_t* choice = reinterpret_cast<uint8_t*>(smem_raw) + (sizeof(int32_t) * P + 15) / 16 * 16;
 
     const int tile = blockIdx.x;
     const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
     const int rows = r1 - r0;
 
     for (int p = threadIdx.x; p < P; p += blockDim.x) inv[p] = -1;
+    stage_map_tile(map, r0, r1, L, choice);  // the walk below turns each map byte into its replica choice in place
     __syncthreads();
     for (int e = threadIdx.x; e < L; e += blockDim.x) {
         const int C = lcnts[e];
@@ -132,7 +154,7 @@ dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_m
         int ordinal = base;
         for (int t = 0; t < rows; ++t) {
             uint8_t c = 0xFF;
-            if (map[static_cast<int64_t>(r0 + t) * L + e]) {
+            if (choice[t * L + e]) {
                 c = static_cast<uint8_t>(replica_index(router, e, ordinal, rqp, D, quota_mode != 0));
                 ++ordinal;
             }
@@ -532,11 +554,14 @@ cudaError_t launch_dense_forward(const Batch<DenseFwdArgs>& b, int L, int P, int
     for (int i = 0; i < b.n; ++i) max_T = b.a[i].T > max_T ? b.a[i].T : max_T;
     if (max_T == 0) return cudaSuccess;
     const dim3 grid(dense_tiles(max_T), b.n);
-    const size_t smem = sizeof(int32_t) * P + static_cast<size_t>(kDenseTileRows) * L + 16;
+    const size_t smem_count = static_cast<size_t>(kDenseTileRows) * L + 16;
+    const size_t smem = (sizeof(int32_t) * P + 15) / 16 * 16 + smem_count;
     cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(dense_scatter_kernel), smem);
     if (e != cudaSuccess) return e;
+    e = ensure_smem_attr(reinterpret_cast<const void*>(dense_count_kernel), smem_count);
+    if (e != cudaSuccess) return e;
     count_launch(2);
-    dense_count_kernel<<<grid, kRerouteThreads, 0, stream>>>(b, L);
+    dense_count_kernel<<<grid, kRerouteThreads, smem_count, stream>>>(b, L);
     dense_scatter_kernel<<<grid, kRerouteThreads, smem, stream>>>(b, L, P, D, quota_mode, interleave);
     return cudaGetLastError();
 }

@@ -182,9 +182,13 @@ class SimGroup:
             int(ids[0].shape[1]), self._stream()), "uep_reroute_sparse")
         return out
 
-    def reroute_dense(self, layer: int, maps: Sequence[torch.Tensor], probs: Sequence[torch.Tensor]):
-        out_maps = [torch.empty((m.shape[0], self.P), dtype=torch.bool, device=self.device) for m in maps]
-        out_probs = [torch.empty((m.shape[0], self.P), dtype=torch.float32, device=self.device) for m in maps]
+    def reroute_dense(self, layer: int, maps: Sequence[torch.Tensor], probs: Sequence[torch.Tensor], out=None):
+        """out: optional (out_probs, out_maps) lists to write into instead of allocating."""
+        if out is None:
+            out_maps = [torch.empty((m.shape[0], self.P), dtype=torch.bool, device=self.device) for m in maps]
+            out_probs = [torch.empty((m.shape[0], self.P), dtype=torch.float32, device=self.device) for m in maps]
+        else:
+            out_probs, out_maps = out
         capi.check(self.lib.uep_reroute_dense_forward(
             self.handle, layer, capi.ptr_array([x.data_ptr() for x in maps]),
             capi.ptr_array([x.data_ptr() for x in probs]), capi.ptr_array([x.data_ptr() for x in out_maps]),
