@@ -8,9 +8,11 @@
 // csrc/ultra_ep.cpp:891-892 of the reference. Here:
 //   * pass 1 counts keys per (tile, expert) from coalesced row reads;
 //   * pass 2 turns the counts of the preceding tiles into a base per expert, resolves
-//     ordinals inside the tile in row-major order (deterministically: per-warp sub-counts,
-//     then match.any inside the warp), and writes every output element exactly once with
-//     coalesced vector stores (zeros included), so no pre-zeroing pass exists.
+//     ordinals inside the tile in row-major order (sparse: per-warp sub-counts, then match.any
+//     inside the warp; dense: the map tile is staged in shared memory, one thread per expert
+//     walks its column only to count, and the replica arithmetic runs over the marked cells
+//     spread over the CTA), and writes every output element exactly once with coalesced
+//     vector stores (zeros included), so no pre-zeroing pass exists.
 // Results equal the reference's dense rule bit for bit; the sparse form applies the same
 // rule per (token, k) entry and therefore is deterministic, which the reference's
 // atomic-counter sparse kernel (reroute.cu:492-515) is not.
@@ -69,6 +71,7 @@ __device__ __forceinline__ Router make_router(int e, const int32_t* lcnts, const
 // ordinal -> replica index (reroute.cu:239-254 of the reference; round-robin: :126)
 __device__ __forceinline__ int replica_index(const Router& r, int e, int ordinal, const int32_t* rqp, int D,
                                              bool quota_mode) {
+    if (r.C <= 1) return 0;  // one instance: every branch below ends at index 0
     if (!quota_mode) return ordinal % r.C;
     int qr = ordinal;
     if (r.stride != 0) qr = static_cast<int>((static_cast<long long>(ordinal) * r.stride + r.offset) % r.total);
@@ -130,35 +133,50 @@ dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_m
     const int vec_ok = ((P & 3) == 0) && ((reinterpret_cast<uintptr_t>(out_probs) & 15u) == 0) &&
                        ((reinterpret_cast<uintptr_t>(out_map) & 3u) == 0);
     extern __shared__ __align__(128) char smem_raw[];
-    // layout: inv[P] int32 | choice[rows][L] uint8
+    // layout: inv[P] int32 | routers[L] | base[L] int32 | choice[rows][L] uint8 (16-byte aligned)
     int32_t* inv = reinterpret_cast<int32_t*>(smem_raw);
-    uint8_t* choice = reinterpret_cast<uint8_t*>(smem_raw) + (sizeof(int32_t) * P + 15) / 16 * 16;
+    Router* routers = reinterpret_cast<Router*>(inv + (P + 3) / 4 * 4);
+    int32_t* base_of = reinterpret_cast<int32_t*>(routers + L);
+    uint8_t* choice = reinterpret_cast<uint8_t*>(base_of + (L + 3) / 4 * 4);
 
     const int tile = blockIdx.x;
     const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
     const int rows = r1 - r0;
 
     for (int p = threadIdx.x; p < P; p += blockDim.x) inv[p] = -1;
-    stage_map_tile(map, r0, r1, L, choice);  // the walk below turns each map byte into its replica choice in place
+    stage_map_tile(map, r0, r1, L, choice);  // the passes below turn each map byte into its replica choice in place
     __syncthreads();
+    // Pass 1, one thread per expert: which slots it owns, its ordinal base in this tile, its routing parameters, and
+    // a walk down its column that only counts: a routed cell of an expert with several instances is marked
+    // 0x80 | (its rank among the tile's routed rows, < 64); with one instance the choice is 0 at once.
     for (int e = threadIdx.x; e < L; e += blockDim.x) {
         const int C = lcnts[e];
         for (int j = 0; j < C; ++j) {
             const int p = l2p[static_cast<int64_t>(e) * D + j];
             if (p >= 0 && p < P) inv[p] = e;
         }
-        // base ordinal of this tile
         int base = 0;
         for (int tl = 0; tl < tile; ++tl) base += tile_counts[static_cast<int64_t>(tl) * L + e];
-        const Router router = make_router(e, lcnts, rqp, D, quota_mode != 0, interleave != 0);
-        int ordinal = base;
+        base_of[e] = base;
+        routers[e] = make_router(e, lcnts, rqp, D, quota_mode != 0, interleave != 0);
+        int seen = 0;
         for (int t = 0; t < rows; ++t) {
             uint8_t c = 0xFF;
             if (choice[t * L + e]) {
-                c = static_cast<uint8_t>(replica_index(router, e, ordinal, rqp, D, quota_mode != 0));
-                ++ordinal;
+                c = C <= 1 ? 0 : static_cast<uint8_t>(0x80 | seen);
+                ++seen;
             }
             choice[t * L + e] = c;
+        }
+    }
+    __syncthreads();
+    // Pass 2, all threads over the tile's cells: the replica arithmetic (a 64-bit multiply and modulo, a prefix
+    // search) only for the marked cells, spread over the CTA instead of sitting in the hot experts' threads.
+    for (int cell = threadIdx.x; cell < rows * L; cell += blockDim.x) {
+        const uint8_t c = choice[cell];
+        if (c >= 0x80 && c != 0xFF) {
+            const int e = cell % L;
+            choice[cell] = static_cast<uint8_t>(replica_index(routers[e], e, base_of[e] + (c & 0x3F), rqp, D, quota_mode != 0));
         }
     }
     __syncthreads();
@@ -555,7 +573,8 @@ cudaError_t launch_dense_forward(const Batch<DenseFwdArgs>& b, int L, int P, int
     if (max_T == 0) return cudaSuccess;
     const dim3 grid(dense_tiles(max_T), b.n);
     const size_t smem_count = static_cast<size_t>(kDenseTileRows) * L + 16;
-    const size_t smem = (sizeof(int32_t) * P + 15) / 16 * 16 + smem_count;
+    static_assert(kDenseTileRows <= 64, "a routed cell's rank inside its tile is kept in six bits");
+    const size_t smem = sizeof(int32_t) * ((P + 3) / 4 * 4) + sizeof(Router) * L + sizeof(int32_t) * ((L + 3) / 4 * 4) + smem_count;
     cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(dense_scatter_kernel), smem);
     if (e != cudaSuccess) return e;
     e = ensure_smem_attr(reinterpret_cast<const void*>(dense_count_kernel), smem_count);
