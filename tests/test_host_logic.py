@@ -183,3 +183,25 @@ def test_expert_load_trace_files(tmp_path, monkeypatch):
     assert len(rows) == len(sent) == 6
     for got, exp in zip(rows, sent):
         assert got[:3] == exp[:3] and np.array_equal(got[3], exp[3]) and np.array_equal(got[4], exp[4])
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs without a GPU (the CPU restatement on host threads) and prints one JSON
+    line with the keys the harness reads."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                          "--cpu-budget-s", "1", "--no-ref", "--config", "cfg1_plan_reroute"],
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "us_per_layer_plan_sync_reroute" and d["unit"] == "us/layer"
+    assert d["higher_is_better"] is False and d["value"] > 0 and d["gpu_launches"] == 0
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"] == {"value": d["value"], "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
