@@ -178,11 +178,16 @@ typedef struct uep_config {
     int32_t quota_kernel_stage;         /* 0 or 1; both give identical plans, accepted for compatibility */
     int32_t grad_reduce_num_sms;        /* even, > 0, clamped to the SM count                */
     int32_t grad_reduce_deterministic;  /* 0 accepted; the fixed-order kernel always runs    */
-    int32_t weight_sync_plan_mode;      /* 0 direct; 1 adaptive: experts with >= relay_min_replicas replicas are relayed
-                                         * (scatter over the replicas + replica-to-replica forward); 2 force relay (>= 2) */
+    int32_t weight_sync_plan_mode;      /* 0 direct; 1 adaptive: experts with >= relay_min_replicas replicas, and the experts of
+                                         * a rank that sends more than any rank receives, are relayed (scatter over the
+                                         * replicas + replica-to-replica forward); 2 force relay (>= 2 replicas) */
     int32_t weight_sync_relay_min_replicas, weight_sync_relay_max_relays, weight_sync_relay_min_fanout_gain;
     int32_t weight_sync_num_sms;        /* CTAs of the copy kernel per rank; 0 = default     */
     int32_t wait_timeout_ms;            /* bound of every device-side wait; 0 = default 5000 */
+    int32_t reroute_max_tokens;         /* > 0: the reroute scratch is sized for this many tokens per rank at creation, so
+                                         * that no reroute call allocates or frees (the reference allocates per call,
+                                         * csrc/ultra_ep.cpp:891-907); 0: grown on demand by the first call that needs more */
+    int32_t reroute_max_topk;           /* top-k bound that goes with reroute_max_tokens (sparse form); 0 = 8 */
 } uep_config;
 
 #define UEP_IPC_HANDLE_BYTES 64
@@ -228,6 +233,12 @@ typedef enum uep_buffer_id {
 } uep_buffer_id;
 int uep_manager_buffer(uep_manager* m, int local_rank, int buffer_id, void** ptr, int* ndim, int64_t shape[3],
                        int64_t stride[3]);
+
+/* Address, in this process, of a PEER rank's replica buffer (UEP_BUF_REPLICA_WEIGHT, _SCALE or _GRAD): the
+ * cudaIpc mapping the manager opened at connect (the rank's own buffer for peer_rank == its rank). What
+ * nvshmem::ptr returns in the reference (csrc/ultra_ep.cpp:400-421); lets other kernels, e.g. the reference's
+ * own copy kernel in a side-by-side measurement, address the same peer memory. */
+int uep_manager_peer_buffer(uep_manager* m, int local_rank, int peer_rank, int buffer_id, void** ptr);
 
 /* Per-call arguments are arrays of length uep_manager_num_local(m): element i belongs to
  * local rank i (a single element in the one-rank-per-process case).
@@ -303,6 +314,13 @@ int uep_debug_withhold_rank(uep_manager* m, int rank);
  * searched, emitted, split). The withhold hook also makes a withheld rank skip publishing its
  * load row. No counterpart in the reference. */
 int uep_debug_sync_trace(uep_manager* m, unsigned long long* host_out, int max_ctas);
+
+/* Measurement aid: time of one one-directional copy of `bytes` bytes (a multiple of 16, at most the replica
+ * weight buffer) from this rank's replica weight buffer into peer_rank's, averaged over `iters` copies on the
+ * communication stream; use_kernel 0: cudaMemcpyAsync (copy engine), 1: a plain load/store kernel. Overwrites
+ * the peer's replica slots; the peer must be idle. Gives the link bandwidth the copy and reduce kernels are
+ * measured against. No counterpart in the reference. */
+int uep_debug_link_probe(uep_manager* m, int peer_rank, int64_t bytes, int iters, int use_kernel, float* ms_out);
 
 /* Counters for benchmarks: kernels launched by this library since the last reset. */
 int64_t uep_launch_count(void);

@@ -59,7 +59,7 @@ class Config(C.Structure):
         ("grad_reduce_deterministic", C.c_int32), ("weight_sync_plan_mode", C.c_int32),
         ("weight_sync_relay_min_replicas", C.c_int32), ("weight_sync_relay_max_relays", C.c_int32),
         ("weight_sync_relay_min_fanout_gain", C.c_int32), ("weight_sync_num_sms", C.c_int32),
-        ("wait_timeout_ms", C.c_int32),
+        ("wait_timeout_ms", C.c_int32), ("reroute_max_tokens", C.c_int32), ("reroute_max_topk", C.c_int32),
     ]
 
 
@@ -91,6 +91,8 @@ SIGNATURES = {
     "uep_manager_num_local": (_i, [_vp]),
     "uep_manager_num_sms": (_i, [_vp]),
     "uep_manager_buffer": (_i, [_vp, _i, _i, C.POINTER(_vp), C.POINTER(_i), C.POINTER(_i64), C.POINTER(_i64)]),
+    "uep_manager_peer_buffer": (_i, [_vp, _i, _i, _i, C.POINTER(_vp)]),
+    "uep_debug_link_probe": (_i, [_vp, _i, _i64, _i, _i, C.POINTER(C.c_float)]),
     "uep_update_placement": (_i, [_vp, _i, _i, C.POINTER(_vp), C.POINTER(_i), _i, _vp]),
     "uep_weight_sync": (_i, [_vp, _i] + [C.POINTER(_vp)] * 4 + [_vp, _i, _vp, C.POINTER(_vp)]),
     "uep_grad_reduce": (_i, [_vp, _i] + [C.POINTER(_vp)] * 2 + [_vp, _i, _vp, C.POINTER(_vp)]),

@@ -9,16 +9,20 @@
 // replica sub-tile at a time through a single shared-memory buffer (load, wait, add, zero
 // with per-thread stores, repeat). Here:
 //   * no task list: every CTA derives the pull list from the plan rows with a block scan;
-//   * accumulators live in registers (16 floats per thread per 16 KiB tile);
-//   * an elected thread keeps a 7-stage ring of 16 KiB bulk loads in flight; the master tile
-//     travels through the same ring in front of its replicas, so no thread ever waits on a
-//     plain global load, and the 112 KiB per CTA (4.7 MB over the default 42 CTAs) cover the
-//     bandwidth-delay product of an NVLink read (about 770 GB/s x 3.5 us);
-//   * the consumed region is zeroed with one bulk store from a zero-filled shared buffer
-//     instead of 256 threads of vector stores;
+//   * roles are split. Two producer warps (one lane each) only issue bulk copies: one feeds the
+//     ring of replica tiles and, once a stage has been consumed, zeroes the region it came from
+//     with a bulk store from a zero tile; the other feeds the ring of master tiles. Eight
+//     consumer warps wait on a stage's "full" mbarrier, add it into accumulators in registers
+//     (16 floats per thread per tile) and arrive on its "empty" mbarrier: there is no CTA-wide
+//     barrier per stage;
+//   * two rings of 16 KiB stages: nine for the REMOTE replica tiles (144 KiB in flight per CTA,
+//     6 MB over the default 42 CTAs: the bandwidth-delay product of NVLink reads under load is
+//     several MB) and three for the local master tiles. In one common ring a master tile would
+//     hold a stage as long as a remote tile does, and with one replica per master half of the
+//     ring would be taken away from the remote loads;
 //   * tiles are interleaved over masters so that concurrent CTAs pull from different peers.
 // The CTA budget (SMs used while the backward pass runs next to it) is the caller's knob
-// (grad_reduce_num_sms); each CTA holds 128 KiB of shared memory.
+// (grad_reduce_num_sms); each CTA holds about 222 KiB of shared memory.
 
 #include "internal.h"
 
@@ -26,18 +30,27 @@ namespace uep {
 
 namespace {
 
-constexpr int kReduceThreads = 256;
-constexpr int kReduceTileElems = 4096;  // 16 KiB
+constexpr int kReduceConsumers = 256;
+constexpr int kReduceThreads = kReduceConsumers + 64;  // eight consumer warps + two producer warps (replica ring, master ring)
+constexpr int kReduceTileElems = 4096;                 // 16 KiB
 constexpr int kReduceTileBytes = kReduceTileElems * 4;
-constexpr int kReduceStages = 7;
-constexpr int kReduceVecPerThread = kReduceTileElems / 4 / kReduceThreads;  // float4 per thread per tile
+constexpr int kReduceStages = 9;                       // ring of remote replica tiles
+constexpr int kMasterStages = 3;                       // ring of local master tiles
+constexpr int kReduceZeroBytes = kReduceTileBytes;      // zero tile; a consumed region is cleared with one store
+constexpr int kReduceVecPerThread = kReduceTileElems / 4 / kReduceConsumers;  // float4 per thread per tile
 constexpr int kMaxPulls = kMaxExportsPerDomain;
 
 struct ReduceShared {
-    int n_active, total_reps, vector_ok, error;
+    int n_active, total_reps, vector_ok;
+    volatile int error;
+    int w_a[kReduceThreads / 32], w_r[kReduceThreads / 32];
     short rep_start[kMaxExpertsPerDomain + 1];
     float* rep_base[kMaxPulls];                    // replica slot base in the peer's grad buffer (null: skip)
     float* master[kMaxExpertsPerDomain][2];        // [n_active][fc1, fc2] master gradient base
+    __align__(8) uint64_t full[kReduceStages];     // a remote tile has landed in the stage
+    __align__(8) uint64_t empty[kReduceStages];    // all eight consumer warps are done with the stage
+    __align__(8) uint64_t m_full[kMasterStages];   // the same for the ring of master tiles
+    __align__(8) uint64_t m_empty[kMasterStages];
 };
 
 struct ReduceItem {
@@ -61,26 +74,41 @@ __device__ __forceinline__ ReduceItem decode_item(int64_t idx, int n_active, int
     return it;
 }
 
-__global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall call) {
-    extern __shared__ __align__(128) char smem_raw[];  // [kReduceStages + 1] tiles; the last one stays zero
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(kReduceThreads, 1) grad_reduce_kernel(ReduceCall call) {
+    extern __shared__ __align__(128) char smem_raw[];  // kReduceStages replica tiles, kMasterStages master tiles, the zero tile
     __shared__ ReduceShared sm;
-    __shared__ __align__(8) uint64_t bars[kReduceStages];
 
     const int M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N, nlocal = call.nlocal;
     const int tid = threadIdx.x;
     const int64_t fc1 = call.fc1_numel, fc2 = call.fc2_numel, total_numel = fc1 + fc2;
-    float* zero_tile = reinterpret_cast<float*>(smem_raw + kReduceStages * kReduceTileBytes);
+    char* master_ring = smem_raw + kReduceStages * kReduceTileBytes;
+    char* zero_tile = master_ring + kMasterStages * kReduceTileBytes;
     DeviceStatus* status0 = call.rank[0]->status;
+    auto stamp = [&](int slot) {
+        if (call.trace != nullptr && tid == 0) call.trace[blockIdx.x * 8 + slot] = global_timer_ns();
+    };
+    stamp(0);
 
     if (tid == 0) {
         sm.n_active = 0;
         sm.total_reps = 0;
         sm.vector_ok = ((fc1 & 3) == 0 && (fc2 & 3) == 0) ? 1 : 0;
         sm.error = 0;
-        for (int s = 0; s < kReduceStages; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < kReduceStages; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], kReduceConsumers / 32);
+        }
+        for (int s = 0; s < kMasterStages; ++s) {
+            mbar_init(&sm.m_full[s], 1);
+            mbar_init(&sm.m_empty[s], kReduceConsumers / 32);
+        }
         fence_mbar_init();
     }
-    for (int i = tid; i < kReduceTileElems; i += blockDim.x) zero_tile[i] = 0.f;
+    for (int i = tid; i < kReduceZeroBytes / 4; i += blockDim.x) reinterpret_cast<float*>(zero_tile)[i] = 0.f;
     fence_proxy_async_smem();
     __syncthreads();
 
@@ -110,16 +138,15 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
                 r_incl += orr;
             }
         }
-        __shared__ int w_a[kReduceThreads / 32], w_r[kReduceThreads / 32];
         if (lane == 31) {
-            w_a[warp] = a_incl;
-            w_r[warp] = r_incl;
+            sm.w_a[warp] = a_incl;
+            sm.w_r[warp] = r_incl;
         }
         __syncthreads();
         int a_off = sm.n_active, r_off = sm.total_reps;
         for (int w = 0; w < warp; ++w) {
-            a_off += w_a[w];
-            r_off += w_r[w];
+            a_off += sm.w_a[w];
+            r_off += sm.w_r[w];
         }
         if (act) {
             const int ai = a_off + a_incl - 1;
@@ -151,11 +178,13 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
     }
     if (tid == 0) sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxPulls ? sm.total_reps : kMaxPulls);
     __syncthreads();
+    stamp(1);
     if (sm.n_active == 0) return;
 
+    const int n_active = sm.n_active;
     const int tiles_fc1 = static_cast<int>((fc1 + kReduceTileElems - 1) / kReduceTileElems);
     const int tiles_fc2 = static_cast<int>((fc2 + kReduceTileElems - 1) / kReduceTileElems);
-    const int64_t total_items = static_cast<int64_t>(sm.n_active) * (tiles_fc1 + tiles_fc2);
+    const int64_t total_items = static_cast<int64_t>(n_active) * (tiles_fc1 + tiles_fc2);
     const int64_t first = blockIdx.x, step = gridDim.x;
     const int64_t count = first < total_items ? (total_items - first + step - 1) / step : 0;
 
@@ -167,7 +196,7 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
     if (!sm.vector_ok) {
         // element-wise path for sizes / pointers that are not multiples of 16 bytes
         for (int64_t k = 0; k < count; ++k) {
-            const ReduceItem it = decode_item(first + k * step, sm.n_active, fc1, fc2, tiles_fc1);
+            const ReduceItem it = decode_item(first + k * step, n_active, fc1, fc2, tiles_fc1);
             float* mp = master_ptr(it);
             const int r0 = sm.rep_start[it.active], r1 = sm.rep_start[it.active + 1];
             for (int i = tid; i < it.elems; i += blockDim.x) {
@@ -185,75 +214,131 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
         return;
     }
 
-    // ---- pipelined path -----------------------------------------------------------------
-    // producer cursor (thread 0): the loads of one item are its master tile, then its replicas
-    int64_t prod_k = 0;
-    int prod_r = -1, prod_r_end = -1;  // prod_r < 0: the master tile of item prod_k is next
-    int64_t issued = 0;
-    auto issue = [&](const float* src, int elems) {
-        const int s = static_cast<int>(issued % kReduceStages);
-        const uint32_t bytes = static_cast<uint32_t>(elems) * 4u;
-        mbar_expect_tx(&bars[s], bytes);
-        bulk_load(smem_raw + s * kReduceTileBytes, src, bytes, &bars[s]);
-        ++issued;
-    };
-    auto produce_one = [&]() -> bool {  // thread 0 only; false when nothing is left
-        while (true) {
-            if (prod_k >= count) return false;
-            const ReduceItem it = decode_item(first + prod_k * step, sm.n_active, fc1, fc2, tiles_fc1);
-            if (prod_r < 0) {
-                prod_r = sm.rep_start[it.active];
-                prod_r_end = sm.rep_start[it.active + 1];
-                issue(master_ptr(it), it.elems);
+    if (tid >= kReduceConsumers + 32) {
+        // ---- producer of the master ring: one load per item, in item order -----------------------
+        if (tid != kReduceConsumers + 32) return;
+        int64_t m_issued = 0;
+        for (; m_issued < count; ++m_issued) {
+            const int s = static_cast<int>(m_issued % kMasterStages);
+            if (m_issued >= kMasterStages) {  // the stage's previous tile has been read by every consumer warp
+                const int64_t prev = m_issued - kMasterStages;
+                if (!mbar_wait(&sm.m_empty[s], static_cast<uint32_t>((prev / kMasterStages) & 1), sm.error ? 0 : call.timeout_ns)) {
+                    sm.error = 1;
+                    break;
+                }
+            }
+            const ReduceItem it = decode_item(first + m_issued * step, n_active, fc1, fc2, tiles_fc1);
+            const uint32_t bytes = static_cast<uint32_t>(it.elems) * 4u;
+            mbar_expect_tx(&sm.m_full[s], bytes);
+            bulk_load(master_ring + s * kReduceTileBytes, master_ptr(it), bytes, &sm.m_full[s]);
+        }
+        if (sm.error) {  // loads that never completed must not find the shared memory released under them
+            for (int64_t j = m_issued > kMasterStages ? m_issued - kMasterStages : 0; j < m_issued; ++j) {
+                mbar_wait(&sm.m_full[j % kMasterStages], static_cast<uint32_t>((j / kMasterStages) & 1), call.timeout_ns);
+            }
+        }
+        return;
+    }
+    if (tid >= kReduceConsumers) {
+        // ---- producer of the replica ring: every remote load and every zero store -----------------
+        if (tid != kReduceConsumers) return;
+        // (item, replica) pairs in the order the consumers take them
+        int64_t k_rep = 0;
+        int r_issue = -1, r_issue_end = -1;
+        ReduceItem it_rep{};
+        auto next_replica = [&](float*& src, int& elems) -> bool {
+            while (true) {
+                if (r_issue < 0) {
+                    if (k_rep >= count) return false;
+                    it_rep = decode_item(first + k_rep * step, n_active, fc1, fc2, tiles_fc1);
+                    r_issue = sm.rep_start[it_rep.active];
+                    r_issue_end = sm.rep_start[it_rep.active + 1];
+                }
+                while (r_issue < r_issue_end && sm.rep_base[r_issue] == nullptr) ++r_issue;
+                if (r_issue >= r_issue_end) {
+                    ++k_rep;
+                    r_issue = -1;
+                    continue;
+                }
+                src = replica_ptr(it_rep, r_issue);
+                elems = it_rep.elems;
+                ++r_issue;
                 return true;
             }
-            while (prod_r < prod_r_end && sm.rep_base[prod_r] == nullptr) ++prod_r;
-            if (prod_r >= prod_r_end) {
-                ++prod_k;
-                prod_r = -1;
-                continue;
+        };
+        float* ring_src[kReduceStages];
+        int ring_elems[kReduceStages];
+        int64_t issued = 0, retired = 0;
+        bool more = true;
+        while (true) {
+            while (more && issued - retired < kReduceStages) {
+                float* src = nullptr;
+                int elems = 0;
+                more = next_replica(src, elems);
+                if (!more) break;
+                const int s = static_cast<int>(issued % kReduceStages);
+                ring_src[s] = src;
+                ring_elems[s] = elems;
+                const uint32_t bytes = static_cast<uint32_t>(elems) * 4u;
+                mbar_expect_tx(&sm.full[s], bytes);
+                bulk_load(smem_raw + s * kReduceTileBytes, src, bytes, &sm.full[s]);
+                ++issued;
             }
-            issue(replica_ptr(it, prod_r), it.elems);
-            ++prod_r;
-            return true;
+            if (retired == issued) break;  // every replica tile has been consumed and cleared
+            // the oldest stage: once every consumer warp has read it, clear the region it came from
+            const int s = static_cast<int>(retired % kReduceStages);
+            if (!mbar_wait(&sm.empty[s], static_cast<uint32_t>((retired / kReduceStages) & 1), sm.error ? 0 : call.timeout_ns)) {
+                sm.error = 1;
+                break;
+            }
+            bulk_store(ring_src[s], zero_tile, static_cast<uint32_t>(ring_elems[s]) * 4u);
+            bulk_commit();
+            ++retired;
         }
-    };
-    if (tid == 0) {
-        for (int s = 0; s < kReduceStages; ++s) {
-            if (!produce_one()) break;
+        bulk_wait_all<0>();
+        if (sm.error) {
+            report_error(status0, UEP_DEV_TIMEOUT_COPY, static_cast<int>(retired));
+            for (int64_t j = issued > kReduceStages ? issued - kReduceStages : 0; j < issued; ++j) {
+                mbar_wait(&sm.full[j % kReduceStages], static_cast<uint32_t>((j / kReduceStages) & 1), call.timeout_ns);
+            }
         }
+        __threadfence_system();
+        return;
     }
+
+    // ---- consumer warps ---------------------------------------------------------------------
+    const int lane = tid & 31;
     int64_t consumed = 0;
-    auto wait_stage = [&]() -> const float4* {
-        const int s = static_cast<int>(consumed % kReduceStages);
-        if (!mbar_wait(&bars[s], static_cast<uint32_t>((consumed / kReduceStages) & 1), call.timeout_ns)) {
-            sm.error = 1;  // keep the control flow uniform; the result of this tile is void
-        }
-        return reinterpret_cast<const float4*>(smem_raw + s * kReduceTileBytes);
-    };
+    stamp(2);
     for (int64_t k = 0; k < count; ++k) {
-        const ReduceItem it = decode_item(first + k * step, sm.n_active, fc1, fc2, tiles_fc1);
-        float4* mp = reinterpret_cast<float4*>(master_ptr(it));
+        const ReduceItem it = decode_item(first + k * step, n_active, fc1, fc2, tiles_fc1);
         const int nvec = it.elems >> 2;
         float4 acc[kReduceVecPerThread];
         {
-            const float4* stage = wait_stage();
+            const int s = static_cast<int>(k % kMasterStages);
+            if (!mbar_wait(&sm.m_full[s], static_cast<uint32_t>((k / kMasterStages) & 1), sm.error ? 0 : call.timeout_ns)) {
+                sm.error = 1;  // keep the control flow uniform; the result of this tile is void
+            }
+            const float4* stage = reinterpret_cast<const float4*>(master_ring + s * kReduceTileBytes);
 #pragma unroll
             for (int u = 0; u < kReduceVecPerThread; ++u) {
-                const int i = tid + u * kReduceThreads;
+                const int i = tid + u * kReduceConsumers;
                 acc[u] = i < nvec ? stage[i] : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            ++consumed;
-            __syncthreads();  // the stage is free again
-            if (tid == 0) produce_one();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.m_empty[s]);
         }
         const int r0 = sm.rep_start[it.active], r1 = sm.rep_start[it.active + 1];
         for (int r = r0; r < r1; ++r) {
             if (sm.rep_base[r] == nullptr) continue;
-            const float4* stage = wait_stage();
+            const int s = static_cast<int>(consumed % kReduceStages);
+            if (!mbar_wait(&sm.full[s], static_cast<uint32_t>((consumed / kReduceStages) & 1), sm.error ? 0 : call.timeout_ns)) {
+                sm.error = 1;
+            }
+            const float4* stage = reinterpret_cast<const float4*>(smem_raw + s * kReduceTileBytes);
 #pragma unroll
             for (int u = 0; u < kReduceVecPerThread; ++u) {
-                const int i = tid + u * kReduceThreads;
+                const int i = tid + u * kReduceConsumers;
                 if (i < nvec) {
                     const float4 v = stage[i];
                     acc[u].x = __fadd_rn(acc[u].x, v.x); acc[u].y = __fadd_rn(acc[u].y, v.y);
@@ -261,35 +346,23 @@ __global__ void __launch_bounds__(kReduceThreads) grad_reduce_kernel(ReduceCall 
                 }
             }
             ++consumed;
-            __syncthreads();  // the stage is free again
-            if (tid == 0) {
-                bulk_store(replica_ptr(it, r), zero_tile, static_cast<uint32_t>(it.elems) * 4u);
-                bulk_commit();
-                produce_one();
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.empty[s]);  // this warp no longer reads the stage
         }
+        float4* mp = reinterpret_cast<float4*>(master_ptr(it));
 #pragma unroll
         for (int u = 0; u < kReduceVecPerThread; ++u) {
-            const int i = tid + u * kReduceThreads;
+            const int i = tid + u * kReduceConsumers;
             if (i < nvec) mp[i] = acc[u];
         }
     }
-    if (tid == 0) {
-        bulk_wait_all<0>();
-        if (sm.error) {
-            report_error(status0, UEP_DEV_TIMEOUT_COPY, static_cast<int>(consumed));
-            for (int64_t j = consumed; j < issued; ++j) {
-                mbar_wait(&bars[j % kReduceStages], static_cast<uint32_t>((j / kReduceStages) & 1), call.timeout_ns);
-            }
-        }
-    }
-    __threadfence_system();
+    stamp(3);
 }
 
 }  // namespace
 
 cudaError_t launch_grad_reduce(const ReduceCall& call, cudaStream_t stream) {
-    const size_t smem = static_cast<size_t>(kReduceStages + 1) * kReduceTileBytes;
+    const size_t smem = static_cast<size_t>(kReduceStages + kMasterStages) * kReduceTileBytes + kReduceZeroBytes;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(grad_reduce_kernel),

@@ -18,6 +18,18 @@ int fail_cuda(cudaError_t e, const char* what) {
     g_last_error = std::string("CUDA error ") + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ") in " + what;
     return UEP_ERR_CUDA;
 }
+
+// SM count of the current device (asked once per device; 0 if the device cannot be queried).
+int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n;
+    }
+    return cached[dev];
+}
 }  // namespace uep
 
 extern "C" {

@@ -85,7 +85,8 @@ struct SyncCall {
     int withhold_rank;  // test hook, as in PlanCall
     int relay_min_replicas;  // 0: every master writes all its replicas itself; else experts with at least this many
                              // replicas are scattered over them and forwarded replica to replica
-    int relay_cap;           // tiles per slot the ready-flag table has room for
+    int relay_adaptive;      // 1: also relay the experts of ranks that send more than any rank receives (see weight_sync.cu)
+    int relay_cap;           // chunks per slot the ready-flag table has room for
     uint64_t* sync_epoch;    // the sync epoch counter of the first hosted rank (by value: one load, not two)
     unsigned long long* trace;  // optional: 8 globaltimer stamps per CTA (tuning aid), or null
 };
@@ -103,6 +104,7 @@ struct ReduceCall {
     int64_t fc1_numel, fc2_numel;
     uint64_t timeout_ns;
     int ctas_per_rank;
+    unsigned long long* trace;  // optional: 8 globaltimer stamps per CTA (tuning aid), or null
 };
 cudaError_t launch_grad_reduce(const ReduceCall& call, cudaStream_t stream);
 
@@ -143,6 +145,7 @@ cudaError_t launch_dense_backward(const Batch<DenseBwdArgs>& b, int L, int P, in
 cudaError_t launch_sparse_reroute(const Batch<SparseArgs>& b, int ids_kind, int K, int L, int D, int interleave,
                                   cudaStream_t stream);
 
+int device_sm_count();  // of the current device; launch sizes are multiples of it
 void set_error(const std::string& msg);
 int fail(int code, const std::string& msg);
 int fail_cuda(cudaError_t e, const char* what);

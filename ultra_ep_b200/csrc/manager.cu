@@ -47,8 +47,10 @@ struct RankHost {
     DeviceStatus* status_host = nullptr;        // mapped pinned
     DeviceStatus* status_dev = nullptr;
     RankDev* dev = nullptr;
-    int32_t* scratch = nullptr;
-    int64_t scratch_elems = 0;
+    // reroute scratch (per-tile expert counts), one buffer per form so that a dense and a sparse
+    // reroute of different layers never share one: [0] dense, [1] sparse
+    int32_t* scratch[2] = {nullptr, nullptr};
+    int64_t scratch_elems[2] = {0, 0};
 };
 
 }  // namespace
@@ -118,17 +120,18 @@ int order_after(uep_manager* m, cudaStream_t later, cudaStream_t earlier) {
     return UEP_OK;
 }
 
-int ensure_scratch(uep_manager* m, RankHost& r, int64_t elems) {
-    if (elems <= r.scratch_elems) return UEP_OK;
-    // Growing is rare (first call at a new token count). cudaFree waits for the device,
-    // so no kernel can still be using the old buffer.
-    if (r.scratch != nullptr) UEP_CUDA_TRY(cudaFree(r.scratch));
-    r.scratch = nullptr;
-    r.scratch_elems = 0;
+// `which`: 0 dense, 1 sparse. With reroute_max_tokens set at creation the buffers already have their
+// final size and this never allocates; otherwise a first call at a larger token count grows the buffer
+// (cudaFree waits for the device, so no kernel can still be using the old one; not allowed while a
+// stream is being captured: make a warm-up call at the largest size first).
+int ensure_scratch(RankHost& r, int which, int64_t elems) {
+    if (elems <= r.scratch_elems[which]) return UEP_OK;
+    if (r.scratch[which] != nullptr) UEP_CUDA_TRY(cudaFree(r.scratch[which]));
+    r.scratch[which] = nullptr;
+    r.scratch_elems[which] = 0;
     const int64_t want = elems + elems / 4;
-    UEP_CUDA_TRY(cudaMalloc(&r.scratch, sizeof(int32_t) * want));
-    r.scratch_elems = want;
-    (void)m;
+    UEP_CUDA_TRY(cudaMalloc(&r.scratch[which], sizeof(int32_t) * want));
+    r.scratch_elems[which] = want;
     return UEP_OK;
 }
 
@@ -175,7 +178,8 @@ void free_rank(RankHost& r, int my_rank_count) {
     cudaFree(r.global_loads);
     cudaFree(r.loads_per_rank);
     cudaFree(r.dev);
-    cudaFree(r.scratch);
+    cudaFree(r.scratch[0]);
+    cudaFree(r.scratch[1]);
     if (r.status_host != nullptr) cudaFreeHost(r.status_host);
     r = RankHost{};
 }
@@ -233,6 +237,7 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
     if (cfg->weight_sync_relay_min_replicas < 0 || cfg->weight_sync_relay_max_relays < 1 || cfg->weight_sync_relay_min_fanout_gain < 0)
         return fail(UEP_ERR_INVALID, "manager_create: bad relay parameters");
     if (cfg->grad_reduce_num_sms <= 0 || cfg->grad_reduce_num_sms % 2 != 0) return fail(UEP_ERR_INVALID, "manager_create: grad_reduce_num_sms must be positive and even");
+    if (cfg->reroute_max_tokens < 0 || cfg->reroute_max_topk < 0) return fail(UEP_ERR_INVALID, "manager_create: negative reroute bounds");
     const int64_t fc1B = cfg->expert_fc1_numel * cfg->weight_data_element_bytes;
     const int64_t fc2B = cfg->expert_fc2_numel * cfg->weight_data_element_bytes;
     if (fc1B % 16 != 0 || fc2B % 16 != 0) return fail(UEP_ERR_INVALID, "manager_create: weight shard bytes must be multiples of 16");
@@ -335,6 +340,12 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
         r.status_host->code = 0;
         r.status_host->detail = 0;
         UEP_TRY_BAIL(cudaHostGetDevicePointer(reinterpret_cast<void**>(&r.status_dev), r.status_host, 0));
+        if (cfg->reroute_max_tokens > 0) {  // final size now: no reroute call allocates or frees afterwards
+            const int64_t topk_bound = cfg->reroute_max_topk > 0 ? cfg->reroute_max_topk : 8;
+            if (ensure_scratch(r, 0, dense_scratch_elems(cfg->reroute_max_tokens, m->L)) != UEP_OK ||
+                ensure_scratch(r, 1, sparse_scratch_elems(static_cast<int64_t>(cfg->reroute_max_tokens) * topk_bound, m->L)) != UEP_OK)
+                return bail(UEP_ERR_CUDA);
+        }
         // masters-only plan in every virtual layer (csrc/ultra_ep.cpp:511-527)
         for (int layer = 0; layer < cfg->num_layers; ++layer) {
             const PlanPtrs p = plan_ptrs(m, r, layer);
@@ -460,6 +471,73 @@ int uep_manager_buffer(uep_manager* m, int local_rank, int buffer_id, void** ptr
     return UEP_OK;
 }
 
+int uep_manager_peer_buffer(uep_manager* m, int local_rank, int peer_rank, int buffer_id, void** ptr) {
+    if (m == nullptr || ptr == nullptr) return fail(UEP_ERR_INVALID, "manager_peer_buffer: null argument");
+    if (!m->connected) return fail(UEP_ERR_STATE, "manager_peer_buffer: manager is not connected");
+    if (local_rank < 0 || local_rank >= m->nlocal || peer_rank < 0 || peer_rank >= m->N)
+        return fail(UEP_ERR_INVALID, "manager_peer_buffer: rank out of range");
+    uint8_t* base = static_cast<uint8_t*>(m->ranks[local_rank].peer_arena[peer_rank]);
+    switch (buffer_id) {
+        case UEP_BUF_REPLICA_WEIGHT: *ptr = base + m->arena.replica_weight; break;
+        case UEP_BUF_REPLICA_SCALE: *ptr = base + m->arena.replica_scale; break;
+        case UEP_BUF_REPLICA_GRAD:
+            if (!m->cfg.is_train) return fail(UEP_ERR_STATE, "Grad buffer not available in inference mode");
+            *ptr = base + m->arena.replica_grad;
+            break;
+        default: return fail(UEP_ERR_INVALID, "manager_peer_buffer: only the replica weight, scale and grad buffers are peer-visible");
+    }
+    return UEP_OK;
+}
+
+namespace {
+// One-directional copy for the link probe: plain 16-byte loads and streaming stores, enough CTAs to fill the link.
+__global__ void __launch_bounds__(256) probe_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int64_t nvec) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        const uint4 a = ld_global_nc_v4(src + i), b = ld_global_nc_v4(src + i + stride);
+        const uint4 c = ld_global_nc_v4(src + i + 2 * stride), d = ld_global_nc_v4(src + i + 3 * stride);
+        st_global_cs_v4(dst + i, a);
+        st_global_cs_v4(dst + i + stride, b);
+        st_global_cs_v4(dst + i + 2 * stride, c);
+        st_global_cs_v4(dst + i + 3 * stride, d);
+    }
+    for (; i < nvec; i += stride) st_global_cs_v4(dst + i, ld_global_nc_v4(src + i));
+}
+}  // namespace
+
+int uep_debug_link_probe(uep_manager* m, int peer_rank, int64_t bytes, int iters, int use_kernel, float* ms_out) {
+    if (m == nullptr || ms_out == nullptr) return fail(UEP_ERR_INVALID, "link_probe: null argument");
+    if (!m->connected || m->nlocal != 1) return fail(UEP_ERR_STATE, "link_probe: needs a connected one-rank-per-process manager");
+    if (peer_rank < 0 || peer_rank >= m->N || peer_rank == m->ranks[0].rank) return fail(UEP_ERR_INVALID, "link_probe: peer must be another rank");
+    const int64_t region = static_cast<int64_t>(m->R) * m->weight_stride;
+    if (bytes <= 0 || bytes > region || bytes % 16 != 0 || iters <= 0) return fail(UEP_ERR_INVALID, "link_probe: bytes must be a positive multiple of 16 within the replica weight buffer");
+    RankHost& r = m->ranks[0];
+    const uint8_t* src = r.arena + m->arena.replica_weight;
+    uint8_t* dst = static_cast<uint8_t*>(r.peer_arena[peer_rank]) + m->arena.replica_weight;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    UEP_CUDA_TRY(cudaEventCreate(&e0));
+    UEP_CUDA_TRY(cudaEventCreate(&e1));
+    cudaStream_t st = m->comm_stream;
+    auto once = [&]() -> cudaError_t {
+        if (!use_kernel) return cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice, st);
+        probe_copy_kernel<<<m->num_sms * 8, 256, 0, st>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), bytes / 16);
+        return cudaGetLastError();
+    };
+    cudaError_t e = once();  // warm-up
+    if (e == cudaSuccess) e = cudaEventRecord(e0, st);
+    for (int i = 0; i < iters && e == cudaSuccess; ++i) e = once();
+    if (e == cudaSuccess) e = cudaEventRecord(e1, st);
+    if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (e != cudaSuccess) return fail_cuda(e, "link_probe");
+    *ms_out = ms / static_cast<float>(iters);
+    return UEP_OK;
+}
+
 int uep_update_placement(uep_manager* m, int layer_id, int input_kind, const void* const* inputs, const int* T,
                          int K_or_L, void* stream_) {
     int rc = check_layer(m, layer_id, "update_placement");
@@ -541,10 +619,12 @@ int uep_weight_sync(uep_manager* m, int layer_id, const int64_t* const* fc1_ptrs
     call.timeout_ns = m->timeout_ns;
     call.ctas_per_rank = m->weight_sync_ctas;
     call.withhold_rank = m->withhold_rank;
-    // plan mode 0: every master writes all its replicas; 1: experts with at least relay_min_replicas replicas are
-    // scattered over their replicas and forwarded replica to replica; 2: every expert with two or more replicas is
+    // plan mode 0: every master writes all its replicas; 1 (adaptive): experts with at least relay_min_replicas
+    // replicas, and the experts of a rank whose outbound volume exceeds every rank's inbound volume, are scattered
+    // over their replicas and forwarded replica to replica; 2: every expert with two or more replicas is
     const int mode = m->cfg.weight_sync_plan_mode;
     call.relay_min_replicas = mode == 0 ? 0 : (mode == 2 ? 2 : std::max(2, m->cfg.weight_sync_relay_min_replicas));
+    call.relay_adaptive = mode == 1 ? 1 : 0;
     call.relay_cap = m->relay_cap;
     call.sync_epoch = m->ranks[0].epochs + 1;
     call.trace = m->sync_trace;
@@ -583,6 +663,7 @@ int uep_grad_reduce(uep_manager* m, int layer_id, const int64_t* const* fc1_grad
     call.timeout_ns = m->timeout_ns;
     // one CTA per SM at most (128 KiB of shared memory each): hosted ranks share the device's SMs
     call.ctas_per_rank = std::max(1, std::min(m->grad_reduce_ctas, m->num_sms / m->nlocal));
+    call.trace = m->sync_trace;
     if (m->R > 0 && m->total_numel > 0) UEP_CUDA_TRY(launch_grad_reduce(call, m->comm_stream));
     return finish_sync_op(m, async_finish, current, done_event);
 }
@@ -602,10 +683,10 @@ int uep_reroute_dense_forward(uep_manager* m, int layer_id, const uint8_t* const
         if (T[i] < 0) return fail(UEP_ERR_INVALID, "dense_reroute_forward: negative token count");
         if (T[i] > 0 && (!routing_maps[i] || !probs[i] || !expanded_maps[i] || !expanded_probs[i]))
             return fail(UEP_ERR_INVALID, "dense_reroute_forward: null tensor");
-        rc = ensure_scratch(m, m->ranks[i], dense_scratch_elems(T[i], m->L));
+        rc = ensure_scratch(m->ranks[i], 0, dense_scratch_elems(T[i], m->L));
         if (rc != UEP_OK) return rc;
         const PlanPtrs p = plan_ptrs(m, m->ranks[i], layer_id);
-        b.a[i] = DenseFwdArgs{routing_maps[i], probs[i], p.l2p, p.lcnts, p.rank_quota_prefix, m->ranks[i].scratch,
+        b.a[i] = DenseFwdArgs{routing_maps[i], probs[i], p.l2p, p.lcnts, p.rank_quota_prefix, m->ranks[i].scratch[0],
                               expanded_maps[i], expanded_probs[i], T[i]};
     }
     // legacy placement has no quotas: its reroute is round-robin over an expert's instances
@@ -646,10 +727,10 @@ int uep_reroute_sparse(uep_manager* m, int layer_id, int ids_kind, const void* c
     for (int i = 0; i < m->nlocal; ++i) {
         if (T[i] < 0) return fail(UEP_ERR_INVALID, "reroute_sparse: negative token count");
         if (static_cast<int64_t>(T[i]) * K > 0 && (!ids[i] || !out[i])) return fail(UEP_ERR_INVALID, "reroute_sparse: null tensor");
-        rc = ensure_scratch(m, m->ranks[i], sparse_scratch_elems(static_cast<int64_t>(T[i]) * K, m->L));
+        rc = ensure_scratch(m->ranks[i], 1, sparse_scratch_elems(static_cast<int64_t>(T[i]) * K, m->L));
         if (rc != UEP_OK) return rc;
         const PlanPtrs p = plan_ptrs(m, m->ranks[i], layer_id);
-        b.a[i] = SparseArgs{ids[i], out[i], p.l2p, p.lcnts, p.rank_quota_prefix, m->ranks[i].scratch, T[i]};
+        b.a[i] = SparseArgs{ids[i], out[i], p.l2p, p.lcnts, p.rank_quota_prefix, m->ranks[i].scratch[1], T[i]};
     }
     UEP_CUDA_TRY(launch_sparse_reroute(b, ids_kind, K, m->L, m->D, m->cfg.legacy_placement ? 2 : m->cfg.solver.reroute_interleave, stream));
     return UEP_OK;

@@ -381,7 +381,7 @@ static int histogram_common(int kind, const void* input, int T, int K_or_L, int 
     const int64_t n = static_cast<int64_t>(T) * K_or_L;
     if (n == 0) return UEP_OK;
     if (input == nullptr) return fail(UEP_ERR_INVALID, "histogram: null input");
-    const int ctas = plan_ctas_per_rank(kind, T, K_or_L, 1, 148);
+    const int ctas = plan_ctas_per_rank(kind, T, K_or_L, 1, std::max(device_sm_count(), 1));
     const size_t smem = sizeof(int32_t) * L;
     UEP_CUDA_TRY(ensure_smem(reinterpret_cast<const void*>(histogram_kernel), smem));
     count_launch();

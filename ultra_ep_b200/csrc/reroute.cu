@@ -17,8 +17,10 @@
 // rule per (token, k) entry and therefore is deterministic, which the reference's
 // atomic-counter sparse kernel (reroute.cu:492-515) is not.
 
+#include <cstdlib>
 #include <mutex>
 #include <string>
+#include <utility>
 
 #include "internal.h"
 
@@ -44,42 +46,77 @@ struct Router {
     int C, total, stride, offset;
 };
 
-__device__ __forceinline__ Router make_router(int e, const int32_t* lcnts, const int32_t* rqp, int D, bool quota_mode,
-                                              bool interleave) {
-    Router r;
-    r.C = lcnts[e];
-    r.total = 0;
-    r.stride = 1;
-    r.offset = 0;
-    if (quota_mode && r.C > 0) r.total = rqp[static_cast<int64_t>(e) * D + r.C - 1];
-    if (quota_mode && interleave && r.total > 1) {
-        int s = r.total / 2 + 1;
-        if (s >= r.total) s = r.total - 1;
-        if (s < 1) s = 1;
-        while (gcd_int(s, r.total) != 1) {
-            ++s;
-            if (s >= r.total) s = 1;
-        }
-        r.stride = s;
-        r.offset = e % r.total;
-    } else {
-        r.stride = 0;  // marks "no interleave"
-    }
-    return r;
+// (ordinal * stride + offset) mod total; all operands are non-negative. The product fits 32 bits for every
+// realistic token count, where the remainder is one hardware-assisted division instead of the 64-bit routine.
+__device__ __forceinline__ int mod_product(int ordinal, int stride, int offset, int total) {
+    const unsigned long long prod = static_cast<unsigned long long>(static_cast<unsigned>(ordinal)) * static_cast<unsigned>(stride) +
+                                    static_cast<unsigned>(offset);
+    if ((prod >> 32) == 0) return static_cast<int>(static_cast<unsigned>(prod) % static_cast<unsigned>(total));
+    return static_cast<int>(prod % static_cast<unsigned long long>(total));
 }
 
-// ordinal -> replica index (reroute.cu:239-254 of the reference; round-robin: :126)
-__device__ __forceinline__ int replica_index(const Router& r, int e, int ordinal, const int32_t* rqp, int D,
-                                             bool quota_mode) {
+// ordinal -> replica index (reroute.cu:239-254 of the reference; round-robin: :126). `prefix` is the expert's
+// row of inclusive rank-quota prefixes (at least C entries).
+__device__ __forceinline__ int replica_index(const Router& r, int ordinal, const int32_t* prefix, bool quota_mode) {
     if (r.C <= 1) return 0;  // one instance: every branch below ends at index 0
     if (!quota_mode) return ordinal % r.C;
     int qr = ordinal;
-    if (r.stride != 0) qr = static_cast<int>((static_cast<long long>(ordinal) * r.stride + r.offset) % r.total);
-    const int32_t* prefix = rqp + static_cast<int64_t>(e) * D;
+    if (r.stride != 0) qr = mod_product(ordinal, r.stride, r.offset, r.total);
     int idx = 0;
     for (int j = 0; j < r.C; ++j) idx += (qr >= prefix[j]) ? 1 : 0;
     return min(idx, max(r.C - 1, 0));
 }
+
+// The first kStagedReps entries of every expert's plan rows (rank-quota prefixes and physical ids) are copied
+// into shared memory once per CTA: resolving an entry then costs no global load. Experts with more instances
+// than that read their rows from global memory.
+constexpr int kStagedReps = 8;
+
+// Thread-per-expert set-up: routing parameters and the staged rows; every global load of an expert is issued
+// before the first one is used (two dependent round trips in all: the count, then the rows).
+__device__ __forceinline__ void stage_expert(int e, const int32_t* __restrict__ lcnts, const int32_t* __restrict__ rqp,
+                                             const int32_t* __restrict__ l2p, int D, bool quota_mode, bool interleave,
+                                             Router* routers, int32_t* prefix_s, int32_t* l2p_s) {
+    Router r;
+    r.C = lcnts[e];
+    const int n = min(min(r.C, D), kStagedReps);
+    int32_t pre[kStagedReps], phys[kStagedReps];
+    int last = 0;
+#pragma unroll
+    for (int j = 0; j < kStagedReps; ++j) {
+        pre[j] = (j < n && quota_mode) ? rqp[static_cast<int64_t>(e) * D + j] : 0;
+        phys[j] = j < n ? l2p[static_cast<int64_t>(e) * D + j] : -1;
+    }
+    if (quota_mode && r.C > kStagedReps) last = rqp[static_cast<int64_t>(e) * D + r.C - 1];
+#pragma unroll
+    for (int j = 0; j < kStagedReps; ++j) {
+        prefix_s[e * kStagedReps + j] = pre[j];
+        l2p_s[e * kStagedReps + j] = phys[j];
+        if (j == r.C - 1) last = pre[j];
+    }
+    r.total = (quota_mode && r.C > 0) ? last : 0;
+    r.stride = 0;  // marks "no interleave"
+    r.offset = 0;
+    if (quota_mode && interleave && r.total > 1) {
+        int st = r.total / 2 + 1;
+        if (st >= r.total) st = r.total - 1;
+        if (st < 1) st = 1;
+        while (gcd_int(st, r.total) != 1) {
+            ++st;
+            if (st >= r.total) st = 1;
+        }
+        r.stride = st;
+        r.offset = e % r.total;
+    }
+    routers[e] = r;
+}
+
+// Programmatic dependent launch: the second kernel of a pair is launched with the stream-serialisation
+// attribute, so its prologue (everything that does not read the first kernel's output) overlaps the first
+// kernel. `pdl_wait` returns once the first kernel has completed and its writes are visible; without the
+// launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------- dense
 // Copies rows [r0, r1) of the bool map into shared memory, 16 bytes per thread when the tile starts on a
@@ -100,125 +137,290 @@ __device__ __forceinline__ void stage_map_tile(const uint8_t* __restrict__ map, 
     for (int i = done + threadIdx.x; i < bytes; i += blockDim.x) smap[i] = src[i];
 }
 
+// The count of a (tile, expert) pair is at most kDenseTileRows = 64: it is kept in ONE BYTE, row-major
+// [tile][L] in the scratch buffer, so that the second kernel can add up the tiles in front of it sixteen
+// experts per load. `fast`: L is a multiple of 16 with L/16 in {1,2,4,...,32}, the map and the scratch are
+// 16-byte aligned: a thread then always meets the same sixteen columns and can add map bytes as packed words.
+__device__ __forceinline__ bool dense_fast_path(const uint8_t* map, const void* scratch, int L) {
+    const int G = L / 16;
+    return (L % 16 == 0) && G <= 32 && (G & (G - 1)) == 0 &&
+           ((reinterpret_cast<uintptr_t>(map) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0;
+}
+
 __global__ void __launch_bounds__(kRerouteThreads) dense_count_kernel(Batch<DenseFwdArgs> batch, int L) {
-    extern __shared__ __align__(128) char smem_raw[];  // [kDenseTileRows][L] bytes
+    pdl_launch_dependents();  // the scatter kernel may start its prologue now
+    extern __shared__ __align__(128) char smem_raw[];  // fast: [L/4] packed words; else [kDenseTileRows][L] bytes
     const DenseFwdArgs& a = batch.a[blockIdx.y];
     const int T = a.T;
     const int tile = blockIdx.x;
     const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
     if (r0 >= T) return;
+    uint8_t* counts = reinterpret_cast<uint8_t*>(a.scratch) + static_cast<int64_t>(tile) * L;
+    if (dense_fast_path(a.map, a.scratch, L)) {
+        const int G = L / 16;
+        uint32_t* cnt = reinterpret_cast<uint32_t*>(smem_raw);
+        for (int i = threadIdx.x; i < L / 4; i += blockDim.x) cnt[i] = 0;
+        __syncthreads();
+        // vector i of the tile covers row i / G, columns 16 * (i % G) ..; blockDim is a multiple of G, so a
+        // thread always meets the same column group and adds the 0/1 bytes of its rows as packed words
+        const uint8_t* src = a.map + static_cast<int64_t>(r0) * L;
+        const int nvec = (r1 - r0) * G;
+        uint4 acc = make_uint4(0, 0, 0, 0);
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            const uint4 v = ld_global_nc_v4(src + static_cast<int64_t>(i) * 16);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        // lanes with the same column group inside the warp
+        for (int d = G; d < 32; d <<= 1) {
+            acc.x += __shfl_xor_sync(kFullMask, acc.x, d); acc.y += __shfl_xor_sync(kFullMask, acc.y, d);
+            acc.z += __shfl_xor_sync(kFullMask, acc.z, d); acc.w += __shfl_xor_sync(kFullMask, acc.w, d);
+        }
+        const int lane = threadIdx.x & 31;
+        if (lane < G) {  // a byte never exceeds 64, so packed adds cannot carry into the next byte
+            atomicAdd(cnt + lane * 4 + 0, acc.x); atomicAdd(cnt + lane * 4 + 1, acc.y);
+            atomicAdd(cnt + lane * 4 + 2, acc.z); atomicAdd(cnt + lane * 4 + 3, acc.w);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < L / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(counts)[i] = cnt[i];
+        return;
+    }
     uint8_t* smap = reinterpret_cast<uint8_t*>(smem_raw);
     stage_map_tile(a.map, r0, r1, L, smap);
     __syncthreads();
     for (int e = threadIdx.x; e < L; e += blockDim.x) {
         int c = 0;
         for (int t = 0; t < r1 - r0; ++t) c += smap[t * L + e] ? 1 : 0;
-        a.scratch[static_cast<int64_t>(tile) * L + e] = c;
+        counts[e] = static_cast<uint8_t>(c);
     }
 }
 
+// Second kernel: one CTA per tile of 64 tokens builds the tile of both outputs in shared memory (zeros,
+// then the tile's routed cells: 64 x top-k of them, against 64 x P output elements) and writes it out with
+// bulk stores. Only the probabilities of routed cells are read. Outputs wider than kDenseMaxChunkCols
+// columns are produced in column chunks.
+constexpr int kDenseMaxChunkCols = 512;
+
+// Row stride of the staged map tile: 16 bytes of padding keep the row starts 16-byte aligned and spread the
+// rows over the shared-memory banks when a thread per row walks across the columns.
+__host__ __device__ __forceinline__ int dense_row_stride(int L) { return (L + 15) / 16 * 16 + 16; }
+
 __global__ void __launch_bounds__(kRerouteThreads)
-dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_mode, int interleave) {
+dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_mode, int interleave, int chunk_cols) {
     const DenseFwdArgs& a = batch.a[blockIdx.y];
     const uint8_t* __restrict__ map = a.map;
     const float* __restrict__ probs = a.probs;
     const int32_t* __restrict__ l2p = a.l2p;
     const int32_t* __restrict__ lcnts = a.lcnts;
     const int32_t* __restrict__ rqp = a.rqp;
-    const int32_t* __restrict__ tile_counts = a.scratch;
     uint8_t* __restrict__ out_map = a.out_map;
     float* __restrict__ out_probs = a.out_probs;
     const int T = a.T;
     if (static_cast<int>(blockIdx.x) * kDenseTileRows >= T) return;
-    const int vec_ok = ((P & 3) == 0) && ((reinterpret_cast<uintptr_t>(out_probs) & 15u) == 0) &&
-                       ((reinterpret_cast<uintptr_t>(out_map) & 3u) == 0);
     extern __shared__ __align__(128) char smem_raw[];
-    // layout: inv[P] int32 | routers[L] | base[L] int32 | choice[rows][L] uint8 (16-byte aligned)
-    int32_t* inv = reinterpret_cast<int32_t*>(smem_raw);
-    Router* routers = reinterpret_cast<Router*>(inv + (P + 3) / 4 * 4);
+    // layout: probs tile [64][chunk] f32 | map tile [64][chunk] u8 | choice [64][Ls] u8 | routers[L] | base[L] i32 |
+    //         prefix rows [L][8] i32 | l2p rows [L][8] i32
+    const int Ls = dense_row_stride(L);
+    float* tile_probs = reinterpret_cast<float*>(smem_raw);
+    uint8_t* tile_map = reinterpret_cast<uint8_t*>(tile_probs + static_cast<size_t>(kDenseTileRows) * chunk_cols);
+    uint8_t* choice = tile_map + (static_cast<size_t>(kDenseTileRows) * chunk_cols + 15) / 16 * 16;
+    Router* routers = reinterpret_cast<Router*>(choice + static_cast<size_t>(kDenseTileRows) * Ls);
     int32_t* base_of = reinterpret_cast<int32_t*>(routers + L);
-    uint8_t* choice = reinterpret_cast<uint8_t*>(base_of + (L + 3) / 4 * 4);
+    int32_t* prefix_s = base_of + (L + 3) / 4 * 4;
+    int32_t* l2p_s = prefix_s + static_cast<size_t>(L) * kStagedReps;
 
     const int tile = blockIdx.x;
     const int r0 = tile * kDenseTileRows, r1 = min(r0 + kDenseTileRows, T);
     const int rows = r1 - r0;
+    const int tid = threadIdx.x;
 
-    for (int p = threadIdx.x; p < P; p += blockDim.x) inv[p] = -1;
-    stage_map_tile(map, r0, r1, L, choice);  // the passes below turn each map byte into its replica choice in place
-    __syncthreads();
-    // Pass 1, one thread per expert: which slots it owns, its ordinal base in this tile, its routing parameters, and
-    // a walk down its column that only counts: a routed cell of an expert with several instances is marked
-    // 0x80 | (its rank among the tile's routed rows, < 64); with one instance the choice is 0 at once.
-    for (int e = threadIdx.x; e < L; e += blockDim.x) {
-        const int C = lcnts[e];
-        for (int j = 0; j < C; ++j) {
-            const int p = l2p[static_cast<int64_t>(e) * D + j];
-            if (p >= 0 && p < P) inv[p] = e;
+    auto zero_tile = [&](int cols) {  // both output tiles of the chunk (16-byte stores; the regions are padded)
+        uint4* z = reinterpret_cast<uint4*>(tile_probs);
+        const int n1 = (rows * cols * 4 + 15) / 16;
+        for (int i = tid; i < n1; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+        uint4* zm = reinterpret_cast<uint4*>(tile_map);
+        const int n2 = (rows * cols + 15) / 16;
+        for (int i = tid; i < n2; i += blockDim.x) zm[i] = make_uint4(0, 0, 0, 0);
+    };
+
+    // ---- prologue: nothing here depends on the count kernel ---------------------------------
+    // the map tile, row by row into the padded rows (the passes below turn each map byte into its replica choice in place)
+    {
+        const uint8_t* src = map + static_cast<int64_t>(r0) * L;
+        if ((L % 16) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+            const int G = L / 16;
+            for (int i = tid; i < rows * G; i += blockDim.x) {
+                const int t = i / G, g = i - t * G;
+                *reinterpret_cast<uint4*>(choice + t * Ls + g * 16) = ld_global_nc_v4(src + static_cast<int64_t>(i) * 16);
+            }
+        } else {
+            for (int i = tid; i < rows * L; i += blockDim.x) {
+                const int t = i / L, e = i - t * L;
+                choice[t * Ls + e] = src[i];
+            }
         }
-        int base = 0;
-        for (int tl = 0; tl < tile; ++tl) base += tile_counts[static_cast<int64_t>(tl) * L + e];
-        base_of[e] = base;
-        routers[e] = make_router(e, lcnts, rqp, D, quota_mode != 0, interleave != 0);
+    }
+    for (int e = tid; e < L; e += blockDim.x) {
+        stage_expert(e, lcnts, rqp, l2p, D, quota_mode != 0, interleave != 0, routers, prefix_s, l2p_s);
+        base_of[e] = 0;
+    }
+    {   // the tile's probabilities are needed only after the wait below: ask for their lines now
+        const char* pbase = reinterpret_cast<const char*>(probs + static_cast<int64_t>(r0) * L);
+        const int64_t pbytes = static_cast<int64_t>(rows) * L * 4;
+        for (int64_t off = static_cast<int64_t>(tid) * 128; off < pbytes; off += static_cast<int64_t>(blockDim.x) * 128) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(pbase + off));
+        }
+    }
+    zero_tile(min(chunk_cols, P));
+    __syncthreads();
+    // one thread per expert walks its column only to count: a routed cell of an expert with several instances
+    // is marked 0x80 | (its rank among the tile's routed rows, < 64); with one instance the choice is 0 at once
+    for (int e = tid; e < L; e += blockDim.x) {
+        const int C = routers[e].C;
         int seen = 0;
         for (int t = 0; t < rows; ++t) {
             uint8_t c = 0xFF;
-            if (choice[t * L + e]) {
+            if (choice[t * Ls + e]) {
                 c = C <= 1 ? 0 : static_cast<uint8_t>(0x80 | seen);
                 ++seen;
             }
-            choice[t * L + e] = c;
+            choice[t * Ls + e] = c;
         }
     }
-    __syncthreads();
-    // Pass 2, all threads over the tile's cells: the replica arithmetic (a 64-bit multiply and modulo, a prefix
-    // search) only for the marked cells, spread over the CTA instead of sitting in the hot experts' threads.
-    for (int cell = threadIdx.x; cell < rows * L; cell += blockDim.x) {
-        const uint8_t c = choice[cell];
-        if (c >= 0x80 && c != 0xFF) {
-            const int e = cell % L;
-            choice[cell] = static_cast<uint8_t>(replica_index(routers[e], e, base_of[e] + (c & 0x3F), rqp, D, quota_mode != 0));
-        }
-    }
-    __syncthreads();
-    // every output element of the tile, once
-    if (vec_ok) {
-        const int quads = P / 4;
-        for (int idx = threadIdx.x; idx < rows * quads; idx += blockDim.x) {
-            const int t = idx / quads, p0 = (idx % quads) * 4;
-            float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);
-            uint32_t mv = 0;
-            float* pvf = reinterpret_cast<float*>(&pv);
+
+    // ---- ordinal base of every expert: tokens routed to it in the tiles in front of this one ---
+    pdl_wait();
+    const uint8_t* counts = reinterpret_cast<const uint8_t*>(a.scratch);
+    if (dense_fast_path(map, a.scratch, L)) {
+        const int G = L / 16;
+        const int g = tid % G, sub = tid / G, nsub = blockDim.x / G;
+        // bytes are widened to 16-bit lanes; a lane overflows after 1024 tiles of 64 rows, so it is spilled before
+        uint32_t lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+        const int lane = tid & 31;
+        auto spill = [&]() {
+            // lanes of the warp that hold the same sixteen columns first (their sum stays below 2^16), then one
+            // shared-memory add per column from the first of them
+            for (int d = G; d < 32; d <<= 1) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int e = inv[p0 + k];
-                if (e >= 0) {
-                    const uint8_t c = choice[t * L + e];
-                    if (c != 0xFF && l2p[static_cast<int64_t>(e) * D + c] == p0 + k) {
-                        pvf[k] = probs[static_cast<int64_t>(r0 + t) * L + e];
-                        mv |= 1u << (8 * k);
+                for (int w = 0; w < 4; ++w) {
+                    lo[w] += __shfl_xor_sync(kFullMask, lo[w], d);
+                    hi[w] += __shfl_xor_sync(kFullMask, hi[w], d);
+                }
+            }
+            if (lane < G) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const int e = g * 16 + w * 4;
+                    if (lo[w] & 0xFFFFu) atomicAdd(base_of + e, static_cast<int>(lo[w] & 0xFFFFu));
+                    if (hi[w] & 0xFFFFu) atomicAdd(base_of + e + 1, static_cast<int>(hi[w] & 0xFFFFu));
+                    if (lo[w] >> 16) atomicAdd(base_of + e + 2, static_cast<int>(lo[w] >> 16));
+                    if (hi[w] >> 16) atomicAdd(base_of + e + 3, static_cast<int>(hi[w] >> 16));
+                }
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) lo[w] = hi[w] = 0;
+        };
+        // every thread runs the same number of rounds (the shuffles above need the whole warp)
+        const int rounds = (tile + 4 * nsub - 1) / (4 * nsub);
+        int since = 0;
+        for (int rd = 0; rd < rounds; ++rd) {
+            const int tl0 = sub + rd * 4 * nsub;
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {  // four independent loads in flight
+                const int tl = tl0 + u * nsub;
+                v[u] = tl < tile ? __ldcg(reinterpret_cast<const uint4*>(counts + static_cast<int64_t>(tl) * L) + g)
+                                 : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    lo[w] += w4[w] & 0x00FF00FFu;
+                    hi[w] += (w4[w] >> 8) & 0x00FF00FFu;
+                }
+            }
+            since += 4;
+            if (since >= 4 * G) {  // at most (4G + 4) counts of at most 64 per lane, times 32 / G lanes in the shuffle: < 2^15
+                spill();
+                since = 0;
+            }
+        }
+        spill();
+    } else {
+        for (int e = tid; e < L; e += blockDim.x) {
+            int b = 0;
+#pragma unroll 8
+            for (int tl = 0; tl < tile; ++tl) b += __ldcg(counts + static_cast<int64_t>(tl) * L + e);
+            base_of[e] = b;
+        }
+    }
+    __syncthreads();
+
+    // ---- resolve the marked cells and scatter the routed cells into the output tile. A thread owns one row
+    //      and every (blockDim / rows)-th word of it: a row has top-k routed cells, so the work is even however
+    //      skewed the experts are (a hot expert's column is spread over all rows' threads). --------------------
+    const int words_per_row = (L + 3) / 4;
+    const int row_threads = blockDim.x / kDenseTileRows;  // 4
+    const int my_row = tid % kDenseTileRows, my_first = tid / kDenseTileRows;
+    for (int p_lo = 0; p_lo < P; p_lo += chunk_cols) {
+        const int cols = min(chunk_cols, P - p_lo);
+        if (p_lo > 0) {
+            __syncthreads();  // the previous chunk has left the tile
+            zero_tile(cols);
+            __syncthreads();
+        }
+        if (my_row < rows) {
+            const float* prow = probs + static_cast<int64_t>(r0 + my_row) * L;
+            for (int wd = my_first; wd < words_per_row; wd += row_threads) {
+                const uint32_t word = *reinterpret_cast<const uint32_t*>(choice + my_row * Ls + wd * 4);
+                if (word == 0xFFFFFFFFu) continue;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint8_t c = static_cast<uint8_t>(word >> (8 * k));
+                    const int e = wd * 4 + k;
+                    if (c == 0xFF || e >= L) continue;
+                    const float pv = prow[e];  // issued before the arithmetic below
+                    const Router r = routers[e];
+                    if (p_lo == 0 && c >= 0x80) {
+                        const int32_t* prefix = r.C <= kStagedReps ? prefix_s + e * kStagedReps : rqp + static_cast<int64_t>(e) * D;
+                        c = static_cast<uint8_t>(replica_index(r, base_of[e] + (c & 0x3F), prefix, quota_mode != 0));
+                        choice[my_row * Ls + e] = c;
+                    }
+                    const int phys = c < kStagedReps ? l2p_s[e * kStagedReps + c] : l2p[static_cast<int64_t>(e) * D + c];
+                    const int p = phys - p_lo;
+                    if (p >= 0 && p < cols) {
+                        tile_probs[my_row * cols + p] = pv;
+                        tile_map[my_row * cols + p] = 1;
                     }
                 }
             }
-            const int64_t o = static_cast<int64_t>(r0 + t) * P + p0;
-            *reinterpret_cast<float4*>(out_probs + o) = pv;
-            *reinterpret_cast<uint32_t*>(out_map + o) = mv;
         }
-    } else {
-        for (int idx = threadIdx.x; idx < rows * P; idx += blockDim.x) {
-            const int t = idx / P, p = idx % P;
-            float v = 0.f;
-            uint8_t m = 0;
-            const int e = inv[p];
-            if (e >= 0) {
-                const uint8_t c = choice[t * L + e];
-                if (c != 0xFF && l2p[static_cast<int64_t>(e) * D + c] == p) {
-                    v = probs[static_cast<int64_t>(r0 + t) * L + e];
-                    m = 1;
-                }
+        fence_proxy_async_smem();  // the tile was written with ordinary stores and may leave through bulk stores
+        __syncthreads();
+        // ---- the tile leaves: one bulk store per output when it is a contiguous, 16-byte aligned block ----
+        const int64_t o = static_cast<int64_t>(r0) * P;
+        const bool whole = cols == P;
+        const bool bulk_p = whole && ((rows * P) % 4 == 0) && ((reinterpret_cast<uintptr_t>(out_probs + o) & 15u) == 0);
+        const bool bulk_m = whole && ((rows * P) % 16 == 0) && ((reinterpret_cast<uintptr_t>(out_map + o) & 15u) == 0);
+        if ((bulk_p || bulk_m) && tid == 0) {
+            if (bulk_p) bulk_store(out_probs + o, tile_probs, static_cast<uint32_t>(rows * P * 4));
+            if (bulk_m) bulk_store(out_map + o, tile_map, static_cast<uint32_t>(rows * P));
+            bulk_commit();
+        }
+        if (!bulk_p) {
+            for (int i = tid; i < rows * cols; i += blockDim.x) {
+                const int t = i / cols, p = i - t * cols;
+                out_probs[o + static_cast<int64_t>(t) * P + p_lo + p] = tile_probs[i];
             }
-            out_probs[static_cast<int64_t>(r0 + t) * P + p] = v;
-            out_map[static_cast<int64_t>(r0 + t) * P + p] = m;
         }
+        if (!bulk_m) {
+            for (int i = tid; i < rows * cols; i += blockDim.x) {
+                const int t = i / cols, p = i - t * cols;
+                out_map[o + static_cast<int64_t>(t) * P + p_lo + p] = tile_map[i];
+            }
+        }
+        if ((bulk_p || bulk_m) && tid == 0) bulk_wait_read<0>();  // shared memory must outlive the stores' reads
     }
 }
 
@@ -285,6 +487,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(kRerouteThreads) key_count_kernel(const IdT* __restrict__ keys, int64_t n,
                                                                     int nb_valid, int tail_bucket,
                                                                     int32_t* __restrict__ tile_counts) {
+    pdl_launch_dependents();
     extern __shared__ __align__(128) char smem_raw[];
     int32_t* hist = reinterpret_cast<int32_t*>(smem_raw);
     const int nb = nb_valid + (tail_bucket ? 1 : 0);
@@ -300,29 +503,39 @@ __global__ void __launch_bounds__(kRerouteThreads) key_count_kernel(const IdT* _
     for (int i = threadIdx.x; i < nb; i += blockDim.x) tile_counts[static_cast<int64_t>(blockIdx.x) * nb + i] = hist[i];
 }
 
-// Row-major ordinal of every entry of this CTA's tile inside its bucket. On return
-// `warp_base[w][b]` has been consumed; ordinals are handed to `emit(i, bucket, ordinal)`.
-// warp_base must hold (blockDim/32) * nb ints and already contain, for warp 0, nothing:
-// the function fills it. base[b] = number of entries of bucket b before this tile.
-template <typename IdT, typename Emit>
-__device__ void tile_ordinals(const IdT* keys, int64_t n, int nb_valid, bool tail_bucket,
-                              const int32_t* base, int32_t* warp_base, Emit emit) {
+// Row-major ordinal of every entry of this CTA's tile inside its bucket, in two steps so that the first
+// one (which reads only the keys) can run before the count kernel has finished:
+//   tile_warp_counts: warp_base[w][b] = entries of bucket b in warp w's part of the tile;
+//   tile_resolve:     with base[b] = entries of bucket b in front of this tile, turns the counts into
+//                     running offsets and hands every entry to emit(i, bucket, ordinal).
+// warp_base holds (blockDim/32) * nb ints.
+template <typename IdT>
+__device__ void tile_warp_counts(const IdT* keys, int64_t n, int nb_valid, bool tail_bucket, int32_t* warp_base) {
     const int nb = nb_valid + (tail_bucket ? 1 : 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int per_warp = kSparseTileEntries / nwarps;
     const int64_t tile_begin = static_cast<int64_t>(blockIdx.x) * kSparseTileEntries;
     const int64_t wbegin = min(tile_begin + static_cast<int64_t>(warp) * per_warp, n);
     const int64_t wend = min(wbegin + per_warp, n);
-
     for (int i = threadIdx.x; i < nwarps * nb; i += blockDim.x) warp_base[i] = 0;
     __syncthreads();
-    // A: per-warp counts
     for (int64_t i = wbegin + lane; i < wend; i += kWarp) {
         const int b = key_bucket<IdT>(keys[i], nb_valid, tail_bucket);
         if (b >= 0) atomicAdd(warp_base + warp * nb + b, 1);
     }
     __syncthreads();
-    // B: exclusive scan over warps, seeded with the tile base
+}
+
+template <typename IdT, typename Emit>
+__device__ void tile_resolve(const IdT* keys, int64_t n, int nb_valid, bool tail_bucket, const int32_t* base,
+                             int32_t* warp_base, Emit emit) {
+    const int nb = nb_valid + (tail_bucket ? 1 : 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int per_warp = kSparseTileEntries / nwarps;
+    const int64_t tile_begin = static_cast<int64_t>(blockIdx.x) * kSparseTileEntries;
+    const int64_t wbegin = min(tile_begin + static_cast<int64_t>(warp) * per_warp, n);
+    const int64_t wend = min(wbegin + per_warp, n);
+    // exclusive scan over warps, seeded with the tile base
     for (int b = threadIdx.x; b < nb; b += blockDim.x) {
         int run = base[b];
         for (int w = 0; w < nwarps; ++w) {
@@ -332,7 +545,7 @@ __device__ void tile_ordinals(const IdT* keys, int64_t n, int nb_valid, bool tai
         }
     }
     __syncthreads();
-    // C: in-order resolution inside the warp
+    // in-order resolution inside the warp
     int32_t* mine = warp_base + warp * nb;
     for (int64_t i0 = wbegin; i0 < wend; i0 += kWarp) {
         const int64_t i = i0 + lane;
@@ -354,6 +567,7 @@ __device__ void tile_ordinals(const IdT* keys, int64_t n, int nb_valid, bool tai
 
 template <typename IdT>
 __global__ void __launch_bounds__(kRerouteThreads) sparse_count_kernel(Batch<SparseArgs> batch, int K, int L) {
+    pdl_launch_dependents();  // the reroute kernel may start its prologue now
     extern __shared__ __align__(128) char smem_raw[];
     const SparseArgs& a = batch.a[blockIdx.y];
     const IdT* keys = static_cast<const IdT*>(a.ids);
@@ -385,21 +599,29 @@ sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interlea
     const int32_t* __restrict__ tile_counts = a.scratch;
     const int64_t n = static_cast<int64_t>(a.T) * K;
     if (static_cast<int64_t>(blockIdx.x) * kSparseTileEntries >= n) return;
-    // layout: base[L] | routers[L] | warp_base[nwarps][L]
+    // layout: base[L] | routers[L] | prefix rows [L][8] | l2p rows [L][8] | warp_base[nwarps][L]
     int32_t* base = reinterpret_cast<int32_t*>(smem_raw);
     Router* routers = reinterpret_cast<Router*>(base + L);
-    int32_t* warp_base = reinterpret_cast<int32_t*>(routers + L);
+    int32_t* prefix_s = reinterpret_cast<int32_t*>(routers + L);
+    int32_t* l2p_s = prefix_s + static_cast<size_t>(L) * kStagedReps;
+    int32_t* warp_base = l2p_s + static_cast<size_t>(L) * kStagedReps;
     const int tile = blockIdx.x;
+    // prologue (plan and ids only): routing parameters, staged plan rows and the per-warp counts of this tile
+    for (int e = threadIdx.x; e < L; e += blockDim.x) {
+        stage_expert(e, lcnts, rqp, l2p, D, interleave != 2, interleave == 1, routers, prefix_s, l2p_s);  // 2: round-robin (legacy placement)
+    }
+    tile_warp_counts<IdT>(ids, n, L, false, warp_base);
+    pdl_wait();  // the tile counts of the first kernel are complete from here on
     for (int e = threadIdx.x; e < L; e += blockDim.x) {
         int b = 0;
-        for (int tl = 0; tl < tile; ++tl) b += tile_counts[static_cast<int64_t>(tl) * L + e];
+#pragma unroll 8
+        for (int tl = 0; tl < tile; ++tl) b += __ldcg(tile_counts + static_cast<int64_t>(tl) * L + e);
         base[e] = b;
-        routers[e] = make_router(e, lcnts, rqp, D, interleave != 2, interleave == 1);  // 2: round-robin (legacy placement)
     }
     __syncthreads();
     // ids may alias out: every entry is read and written by the same lane, the write comes
     // last, and tiles do not overlap.
-    tile_ordinals<IdT>(ids, n, L, false, base, warp_base, [&](int64_t i, int b, int ordinal) {
+    tile_resolve<IdT>(ids, n, L, false, base, warp_base, [&](int64_t i, int b, int ordinal) {
         if (b < 0) {
             out[i] = ids[i];
             return;
@@ -409,8 +631,9 @@ sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interlea
             out[i] = ids[i];
             return;
         }
-        const int j = replica_index(r, b, ordinal, rqp, D, interleave != 2);
-        out[i] = static_cast<IdT>(l2p[static_cast<int64_t>(b) * D + j]);
+        const int32_t* prefix = r.C <= kStagedReps ? prefix_s + b * kStagedReps : rqp + static_cast<int64_t>(b) * D;
+        const int j = replica_index(r, ordinal, prefix, interleave != 2);
+        out[i] = static_cast<IdT>(j < kStagedReps ? l2p_s[b * kStagedReps + j] : l2p[static_cast<int64_t>(b) * D + j]);
     });
 }
 
@@ -429,10 +652,13 @@ dispatch_positions_kernel(const int32_t* __restrict__ phys, int64_t n, int P, co
     int32_t* warp_base = totals + nb;
     __shared__ int s_carry;
     const int tile = blockIdx.x;
+    tile_warp_counts<int32_t>(phys, n, P, true, warp_base);
+    pdl_wait();
     for (int b = threadIdx.x; b < nb; b += blockDim.x) {
         int before = 0, total = 0;
+#pragma unroll 8
         for (int tl = 0; tl < num_tiles; ++tl) {
-            const int c = tile_counts[static_cast<int64_t>(tl) * nb + b];
+            const int c = __ldcg(tile_counts + static_cast<int64_t>(tl) * nb + b);
             if (tl < tile) before += c;
             total += c;
         }
@@ -467,8 +693,8 @@ dispatch_positions_kernel(const int32_t* __restrict__ phys, int64_t n, int P, co
         if (threadIdx.x == blockDim.x - 1) s_carry = carry + woff + incl;
         __syncthreads();
     }
-    tile_ordinals<int32_t>(phys, n, P, true, base, warp_base,
-                           [&](int64_t i, int, int ordinal) { pos[i] = ordinal; });
+    tile_resolve<int32_t>(phys, n, P, true, base, warp_base,
+                          [&](int64_t i, int, int ordinal) { pos[i] = ordinal; });
 }
 
 // ------------------------------------------------------------------- row gather (HBM)
@@ -555,7 +781,20 @@ __global__ void __launch_bounds__(256) gather_rows_plain_kernel(const uint8_t* _
 
 cudaError_t ensure_smem_attr(const void* fn, size_t bytes) {
     if (bytes <= 48 * 1024) return cudaSuccess;
-    return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    // remembered per kernel: the attribute is set again only when a launch needs more than any before it
+    static std::mutex mu;
+    static const void* fns[16];
+    static size_t granted[16];
+    static int n = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    int i = 0;
+    while (i < n && fns[i] != fn) ++i;
+    if (i < n && granted[i] >= bytes) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e != cudaSuccess) return e;
+    if (i == n && n < 16) fns[n++] = fn;
+    if (i < 16) granted[i] = bytes;
+    return cudaSuccess;
 }
 
 int dense_tiles(int T) { return (T + kDenseTileRows - 1) / kDenseTileRows; }
@@ -566,23 +805,57 @@ int64_t sparse_tiles(int64_t n) { return (n + kSparseTileEntries - 1) / kSparseT
 int64_t dense_scratch_elems(int T, int L) { return static_cast<int64_t>(dense_tiles(T)) * L + 4; }
 int64_t sparse_scratch_elems(int64_t entries, int L) { return sparse_tiles(entries) * L + 4; }
 
+// Launch of a kernel that may start before the kernel in front of it in the stream has finished
+// (programmatic dependent launch); the kernel calls pdl_wait() before it reads that kernel's output.
+// UEP_DISABLE_PDL=1 turns the attribute off (the pair then runs strictly one after the other).
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+    static const bool disabled = [] {
+        const char* e = std::getenv("UEP_DISABLE_PDL");
+        return e != nullptr && e[0] == '1';
+    }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = disabled ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 cudaError_t launch_dense_forward(const Batch<DenseFwdArgs>& b, int L, int P, int D, int quota_mode, int interleave,
                                  cudaStream_t stream) {
     int max_T = 0;
     for (int i = 0; i < b.n; ++i) max_T = b.a[i].T > max_T ? b.a[i].T : max_T;
     if (max_T == 0) return cudaSuccess;
     const dim3 grid(dense_tiles(max_T), b.n);
-    const size_t smem_count = static_cast<size_t>(kDenseTileRows) * L + 16;
     static_assert(kDenseTileRows <= 64, "a routed cell's rank inside its tile is kept in six bits");
-    const size_t smem = sizeof(int32_t) * ((P + 3) / 4 * 4) + sizeof(Router) * L + sizeof(int32_t) * ((L + 3) / 4 * 4) + smem_count;
+    const size_t smem_count = static_cast<size_t>(kDenseTileRows) * L + 16;
+    // shared memory of the scatter kernel: the map tile, the per-expert tables, and as many output columns
+    // (five bytes per row and column) as fit beside them
+    const size_t fixed = static_cast<size_t>(kDenseTileRows) * dense_row_stride(L) + sizeof(Router) * L +
+                         sizeof(int32_t) * ((L + 3) / 4 * 4) + 2 * sizeof(int32_t) * kStagedReps * L + 64;
+    const size_t budget = 200 * 1024;
+    if (fixed + static_cast<size_t>(kDenseTileRows) * 5 * 16 > budget) return cudaErrorInvalidValue;  // L in the thousands
+    int chunk = static_cast<int>((budget - fixed) / (static_cast<size_t>(kDenseTileRows) * 5));
+    chunk = chunk > kDenseMaxChunkCols ? kDenseMaxChunkCols : chunk;
+    chunk = chunk >= P ? P : chunk / 16 * 16;
+    const size_t smem = static_cast<size_t>(kDenseTileRows) * chunk * 4 + (static_cast<size_t>(kDenseTileRows) * chunk + 15) / 16 * 16 + fixed;
     cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(dense_scatter_kernel), smem);
     if (e != cudaSuccess) return e;
     e = ensure_smem_attr(reinterpret_cast<const void*>(dense_count_kernel), smem_count);
     if (e != cudaSuccess) return e;
     count_launch(2);
     dense_count_kernel<<<grid, kRerouteThreads, smem_count, stream>>>(b, L);
-    dense_scatter_kernel<<<grid, kRerouteThreads, smem, stream>>>(b, L, P, D, quota_mode, interleave);
-    return cudaGetLastError();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return launch_dependent(dense_scatter_kernel, grid, dim3(kRerouteThreads), smem, stream, b, L, P, D, quota_mode,
+                            interleave, chunk);
 }
 
 cudaError_t launch_dense_backward(const Batch<DenseBwdArgs>& b, int L, int P, int D, cudaStream_t stream) {
@@ -590,7 +863,8 @@ cudaError_t launch_dense_backward(const Batch<DenseBwdArgs>& b, int L, int P, in
     for (int i = 0; i < b.n; ++i) max_T = b.a[i].T > max_T ? b.a[i].T : max_T;
     if (max_T == 0) return cudaSuccess;
     int64_t blocks = (static_cast<int64_t>(max_T) * L / 4 + kRerouteThreads - 1) / kRerouteThreads + 1;
-    const int64_t cap = (148 * 16) / b.n > 1 ? (148 * 16) / b.n : 1;
+    const int64_t sms = device_sm_count() > 0 ? device_sm_count() : 1;
+    const int64_t cap = (sms * 16) / b.n > 1 ? (sms * 16) / b.n : 1;
     if (blocks > cap) blocks = cap;
     count_launch();
     dense_backward_kernel<<<dim3(static_cast<unsigned>(blocks), b.n), kRerouteThreads, 0, stream>>>(b, L, P, D);
@@ -608,15 +882,17 @@ static cudaError_t launch_sparse_typed(const Batch<SparseArgs>& b, int K, int L,
     if (max_n == 0) return cudaSuccess;
     const dim3 grid(static_cast<unsigned>(sparse_tiles(max_n)), b.n);
     const size_t smem1 = sizeof(int32_t) * L;
-    const size_t smem2 = sizeof(int32_t) * L + sizeof(Router) * L + sizeof(int32_t) * (kRerouteThreads / 32) * L;
+    const size_t smem2 = sizeof(int32_t) * L + sizeof(Router) * L + 2 * sizeof(int32_t) * kStagedReps * L +
+                         sizeof(int32_t) * (kRerouteThreads / 32) * L;
     cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(sparse_count_kernel<IdT>), smem1);
     if (e != cudaSuccess) return e;
     e = ensure_smem_attr(reinterpret_cast<const void*>(sparse_reroute_kernel<IdT>), smem2);
     if (e != cudaSuccess) return e;
     count_launch(2);
     sparse_count_kernel<IdT><<<grid, kRerouteThreads, smem1, stream>>>(b, K, L);
-    sparse_reroute_kernel<IdT><<<grid, kRerouteThreads, smem2, stream>>>(b, K, L, D, interleave);
-    return cudaGetLastError();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return launch_dependent(sparse_reroute_kernel<IdT>, grid, dim3(kRerouteThreads), smem2, stream, b, K, L, D, interleave);
 }
 
 cudaError_t launch_sparse_reroute(const Batch<SparseArgs>& b, int ids_kind, int K, int L, int D, int interleave,
@@ -672,7 +948,7 @@ static int sparse_common(int kind, const void* ids, void* out, int T, int K, int
                          void* stream_) {
     if (T < 0 || K < 0 || L <= 0 || D < 1) return fail(UEP_ERR_INVALID, "sparse_reroute: bad sizes");
     if (static_cast<int64_t>(T) * K == 0) return UEP_OK;
-    if (!ids || !out || !scratch || !l2p || !lcnts || !rqp) return fail(UEP_ERR_INVALID, "sparse_reroute: null pointer");
+    if (!ids || !out || !scratch || !l2p || !lcnts || (interleave != 2 && !rqp)) return fail(UEP_ERR_INVALID, "sparse_reroute: null pointer");
     Batch<SparseArgs> b{};
     b.n = 1;
     b.a[0] = SparseArgs{ids, out, l2p, lcnts, rqp, scratch, T};
@@ -766,9 +1042,9 @@ int uep_dispatch_positions(const int32_t* phys_ids, int64_t num_entries, int P, 
     UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(dispatch_positions_kernel), smem2));
     count_launch(2);
     key_count_kernel<int32_t><<<tiles, kRerouteThreads, smem1, stream>>>(phys_ids, num_entries, P, 1, scratch);
-    dispatch_positions_kernel<<<tiles, kRerouteThreads, smem2, stream>>>(phys_ids, num_entries, P, scratch, tiles, pos,
-                                                                         expert_offsets);
     UEP_CUDA_TRY(cudaGetLastError());
+    UEP_CUDA_TRY(launch_dependent(dispatch_positions_kernel, dim3(tiles), dim3(kRerouteThreads), smem2, stream, phys_ids,
+                                  num_entries, P, static_cast<const int32_t*>(scratch), tiles, pos, expert_offsets));
     return UEP_OK;
 }
 
@@ -787,12 +1063,14 @@ int uep_gather_rows(const void* in, const int32_t* pos, void* out, int64_t num_r
         const size_t smem = static_cast<size_t>(kGatherStages) * kGatherChunk;
         UEP_CUDA_TRY(ensure_smem_attr(reinterpret_cast<const void*>(gather_rows_kernel), smem));
         int64_t ctas = num_rows * chunks;
-        if (ctas > 2 * 148) ctas = 2 * 148;
+        const int64_t sms = device_sm_count() > 0 ? device_sm_count() : 1;
+        if (ctas > 2 * sms) ctas = 2 * sms;  // two single-thread CTAs per SM
         gather_rows_kernel<<<static_cast<int>(ctas), 32, smem, stream>>>(
             static_cast<const uint8_t*>(in), pos, static_cast<uint8_t*>(out), num_rows, row_bytes, chunks,
             num_src_rows, 2000000000ull, st);
     } else {
-        int64_t ctas = num_rows > 148 * 8 ? 148 * 8 : num_rows;
+        const int64_t sms = device_sm_count() > 0 ? device_sm_count() : 1;
+        int64_t ctas = num_rows > sms * 8 ? sms * 8 : num_rows;
         gather_rows_plain_kernel<<<static_cast<int>(ctas), 256, 0, stream>>>(
             static_cast<const uint8_t*>(in), pos, static_cast<uint8_t*>(out), num_rows, row_bytes, num_src_rows, st);
     }

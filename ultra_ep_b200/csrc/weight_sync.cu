@@ -11,22 +11,31 @@
 //     read from local HBM once (cp.async.bulk global->shared, mbarrier) and stored to each
 //     destination slot (cp.async.bulk shared->global, peer memory over NVLink); loads run
 //     up to three tiles ahead of the stores;
-//   * tiles are interleaved over masters so that concurrent CTAs feed different peers; when
-//     several ranks are hosted on one device their tiles form one pool shared by all CTAs;
-//   * the CTA that finishes last publishes "rank r has delivered epoch e" to the ranks it
-//     sent to (system-scope release) and waits, bounded, for the same word from the ranks
-//     that send to it. When the kernel ends, this rank's replica slots are complete.
+//   * work is handed out by an atomic counter, interleaved over masters so that concurrent
+//     CTAs feed different peers; when several ranks are hosted on one device their work forms
+//     one pool shared by all CTAs;
+//   * the CTA that finishes last issues one system-scope fence and then tells the ranks it
+//     sent to "rank r has delivered epoch e" (relaxed stores), and waits, bounded, for the same
+//     word from the ranks that send to it. When the kernel ends, this rank's replica slots are
+//     complete.
 // Pointers or sizes that are not multiples of 16 bytes take a plain vector/byte copy path.
 //
 // Relay (optional; the reference's relay plan, csrc/kernels/weight_sync.cu:129-191, 295-502,
-// exists only for NVLink domains above 8 ranks). An expert with r >= relay_min_replicas replicas
-// is broadcast as scatter + forward: its master sends tile t only to replica t mod r and raises
-// that tile's ready flag there; every replica forwards the tiles it received from the master to
-// the other r-1 replicas. The master's rank then sends the expert once instead of r times, and
-// the forwarding load is spread over the replicas' ranks. Whether an expert is relayed is a pure
-// function of the plan, so all ranks agree without talking. Forward tiles sit behind all send
-// tiles in the hand-out order: a CTA that waits (bounded) for a ready flag waits for a tile that
-// a running CTA, on this or another device, is already sending.
+// exists only for NVLink domains above 8 ranks and raises one ready flag per chunk of tiles,
+// :638-677). A relayed expert with r replicas is broadcast as scatter + forward in chunks of
+// four tiles (128 KiB): its master sends chunk c only to replica c mod r and raises that chunk's
+// ready flag there once the chunk's stores are complete (one system-scope fence per chunk);
+// every replica forwards the chunks it received from the master to the other r-1 replicas. The
+// master's rank then sends the expert once instead of r times, and the forwarding load is
+// spread over the replicas' ranks. Which experts are relayed is a pure function of the plan and
+// the configuration, so all ranks agree without talking:
+//   * force mode: every expert with at least two replicas;
+//   * adaptive mode: experts with at least relay_min_replicas replicas, and, on a rank whose
+//     outbound volume exceeds the largest inbound volume of any rank in this plan (which no
+//     relaying can reduce), that rank's experts with the most replicas until it no longer does.
+// Relayed chunks are handed out first (a second hop depends on them), then the direct tiles,
+// then the forward chunks: a CTA that waits (bounded) for a ready flag waits for a chunk that a
+// running CTA, on this or another device, is already sending.
 
 #include <cstdio>
 #include <cstdlib>
@@ -42,23 +51,29 @@ constexpr int kMaxSends = kMaxExportsPerDomain;  // replicas of one rank's maste
 constexpr int kMaxFwd = 64;                       // replica slots of the hosted ranks that may forward
 constexpr int kMaxRelayReplicas = 16;
 constexpr int kMaxFwdDst = kMaxFwd * (kMaxRelayReplicas - 1);
+constexpr int kChunkTiles = 4;                    // tiles per relayed chunk (one ready flag per chunk)
 
 struct SyncShared {
     int n_active;          // masters (of all hosted ranks) that have replicas
     int total_reps;        // sum of their replica counts
     int all_aligned;       // every source pointer 16-byte aligned
     int is_last;
+    int n_relay;           // relayed ones among the active masters
     int n_fwd;             // forward entries
-    int fwd_tiles;         // tiles to forward, all entries
+    int fwd_units;         // chunks to forward, all entries
+    int floor_in;          // adaptive relay: the largest inbound expert count of any rank
     unsigned send_mask[kMaxLocalRanks][3];  // per hosted rank: ranks it writes to (as master or as forwarder)
     unsigned recv_mask[kMaxLocalRanks][3];  // per hosted rank: ranks that write to it
     int timeout_peer;
-    int s_tile;
+    int s_unit;
     unsigned long long epoch;
     int shard_tiles[4];
     int w_a[kSyncThreads / 32], w_r[kSyncThreads / 32];
+    int rank_out[kMaxPeers], rank_in[kMaxPeers];  // adaptive relay: experts each rank sends / receives under this plan
     short rep_start[kMaxExpertsPerDomain + 1];  // [n_active+1] offsets into dst_*
+    short order[kMaxExpertsPerDomain];          // hand-out order of the active masters: relayed ones first
     unsigned char relay_r[kMaxExpertsPerDomain];  // [n_active] 0: direct, else the replica count of a relayed expert
+    unsigned char relay_of[kMaxExpertsPerDomain]; // [logical expert of the domain] the same for every expert of the plan
     // Addresses are resolved once per CTA: the issuing thread must not chase pointers
     // through global memory for every 32 KiB tile.
     const uint8_t* src[kMaxExpertsPerDomain][4];  // [n_active][shard] master shard base
@@ -75,19 +90,28 @@ struct SyncShared {
     uint8_t* fwd_src_s[kMaxFwd];
     const uint64_t* fwd_flags[kMaxFwd]; // its row of ready flags
     unsigned char fwd_r[kMaxFwd], fwd_k[kMaxFwd], fwd_lr[kMaxFwd];
-    int fwd_tile_start[kMaxFwd + 1];    // prefix of the tiles each entry forwards
+    int fwd_unit_start[kMaxFwd + 1];    // prefix of the chunks each entry forwards
     short fwd_dst_start[kMaxFwd + 1];
     uint8_t* fwd_dst_w[kMaxFwdDst];
     uint8_t* fwd_dst_s[kMaxFwdDst];
     __align__(8) uint64_t bars[8];
 };
 
+// One unit of work as the counter hands it out.
+struct Unit {
+    int kind;            // 0: one tile of a direct expert; 1: a chunk a master scatters; 2: a chunk a replica forwards
+    int who;             // kind 0/1: index of the active master; kind 2: forward entry
+    int tile, tile_end;  // tile range over the expert's shards
+    int chunk;           // kind 1/2: chunk index (selects the ready flag)
+};
+
 struct TileRef {
-    int active;          // send tile: index of the active master; forward tile: -1 - entry
+    int kind, who;
     int tile_in_expert;  // tile index over the expert's shards
     int shard;           // 0..3
     int64_t offset;      // byte offset inside the shard
     int bytes;           // bytes of this tile
+    int chunk;
 };
 
 template <int kSyncTile>
@@ -101,24 +125,6 @@ __device__ __forceinline__ void locate_tile(TileRef& t, const ShardLayout& sh, c
     t.offset = static_cast<int64_t>(tile) * kSyncTile;
     const int64_t left = sh.bytes[t.shard] - t.offset;
     t.bytes = static_cast<int>(left < kSyncTile ? left : kSyncTile);
-}
-
-// idx < send_tiles: tile idx / n_active of master idx % n_active. Above: the forward tiles, entry after entry.
-template <int kSyncTile, bool kRelay>
-__device__ __forceinline__ TileRef decode_tile(int idx, int send_tiles, const SyncShared& sm, const ShardLayout& sh) {
-    TileRef t;
-    if (!kRelay || idx < send_tiles) {
-        t.active = idx % sm.n_active;
-        t.tile_in_expert = idx / sm.n_active;
-    } else {
-        const int f_idx = idx - send_tiles;
-        int f = 0;
-        while (f + 1 < sm.n_fwd && f_idx >= sm.fwd_tile_start[f + 1]) ++f;
-        t.active = -1 - f;
-        t.tile_in_expert = sm.fwd_k[f] + (f_idx - sm.fwd_tile_start[f]) * sm.fwd_r[f];
-    }
-    locate_tile<kSyncTile>(t, sh, sm.shard_tiles);
-    return t;
 }
 
 __device__ __forceinline__ uint8_t* shard_base(uint8_t* weight_slot, uint8_t* scale_slot, const ShardLayout& sh, int shard) {
@@ -141,10 +147,6 @@ __device__ void copy_plain(const uint8_t* src, uint8_t* dst, int bytes, bool str
     for (int i = done + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = streaming ? src[i] : __ldcg(src + i);
 }
 
-__device__ __forceinline__ bool relayed(int reps, int relay_min) {
-    return relay_min > 0 && reps >= relay_min && reps >= 2 && reps <= kMaxRelayReplicas;
-}
-
 // kRelay = false compiles the relay machinery out: the direct fan-out pays neither for its code nor for
 // its per-tile bookkeeping (the kernel runs once per layer from a cold instruction cache, and the one
 // issuing thread per CTA is on the critical path of every tile).
@@ -158,11 +160,13 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     const ShardLayout& sh = call.shards;
     const int M = call.M, R = call.R, D = call.D, Lp = M + R, N = call.N, nlocal = call.nlocal;
     const int tid = threadIdx.x;
-    // Relaying needs a forward entry per local replica slot; the limit depends on the configuration
-    // only, so every rank comes to the same answer.
+    // Relaying needs a forward entry per local replica slot and a ready flag per chunk; the limits depend on
+    // the configuration only, so every rank comes to the same answer.
     int tiles_per_expert = 0;
     for (int s = 0; s < sh.num_shards; ++s) tiles_per_expert += static_cast<int>((sh.bytes[s] + kSyncTile - 1) / kSyncTile);
-    const int relay_min = (kRelay && nlocal * R <= kMaxFwd && tiles_per_expert <= call.relay_cap) ? call.relay_min_replicas : 0;
+    const int chunks_per_expert = (tiles_per_expert + kChunkTiles - 1) / kChunkTiles;
+    const bool relay_on = kRelay && call.relay_min_replicas > 0 && nlocal * R <= kMaxFwd && chunks_per_expert <= call.relay_cap &&
+                          N * M <= kMaxExpertsPerDomain && N <= kMaxPeers;
     auto stamp = [&](int slot) {
         if (call.trace != nullptr && tid == 0) call.trace[blockIdx.x * 8 + slot] = global_timer_ns();
     };
@@ -174,8 +178,10 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         sm.total_reps = 0;
         sm.all_aligned = 1;
         sm.is_last = 0;
+        sm.n_relay = 0;
         sm.n_fwd = 0;
-        sm.fwd_tiles = 0;
+        sm.fwd_units = 0;
+        sm.floor_in = 1;
         sm.timeout_peer = -1;
         for (int s = 0; s < 4; ++s) shard_tiles[s] = s < sh.num_shards ? static_cast<int>((sh.bytes[s] + kSyncTile - 1) / kSyncTile) : 0;
         for (int s = 0; s < kSyncStages; ++s) mbar_init(&bars[s], 1);
@@ -184,6 +190,12 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     for (int i = tid; i < kMaxLocalRanks * 3; i += blockDim.x) {
         sm.send_mask[i / 3][i % 3] = 0;
         sm.recv_mask[i / 3][i % 3] = 0;
+    }
+    if (kRelay) {
+        for (int i = tid; i < N && i < kMaxPeers; i += blockDim.x) {
+            sm.rank_out[i] = 0;
+            sm.rank_in[i] = 0;
+        }
     }
     __syncthreads();
     // Every global read of the set-up is issued here, before anything depends on one of them, so
@@ -229,6 +241,57 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         sm.peer_flags[tid] = pre_pf;
     }
     if (tid == 0) sm.epoch = pre_epoch + 1;
+
+    // Which experts are relayed: one answer per logical expert, the same on every rank (the plan is).
+    if (kRelay) {
+        const PlanPtrs& plan0 = call.plan[0];
+        const int L = min(N * M, kMaxExpertsPerDomain);
+        for (int l = tid; l < L; l += blockDim.x) {
+            int reps = relay_on ? plan0.lcnts[l] - 1 : 0;
+            reps = reps < 0 ? 0 : (reps > D - 1 ? D - 1 : reps);
+            const bool by_count = reps >= call.relay_min_replicas && reps >= 2 && reps <= kMaxRelayReplicas;
+            sm.relay_of[l] = by_count ? static_cast<unsigned char>(reps) : 0;
+            if (relay_on && call.relay_adaptive && reps > 0) atomicAdd(&sm.rank_out[l / M], reps);
+        }
+        if (relay_on && call.relay_adaptive) {
+            for (int i = tid; i < N * R; i += blockDim.x) {
+                const int r = i / R;
+                if (plan0.p2l[r * Lp + M + i % R] >= 0) atomicAdd(&sm.rank_in[r], 1);
+            }
+        }
+        __syncthreads();
+        if (relay_on && call.relay_adaptive) {
+            if (tid < 32) {  // the inbound volume no relaying can reduce
+                int mx = 1;
+                for (int r = tid; r < N; r += 32) mx = max(mx, sm.rank_in[r]);
+                mx = warp_max(mx);
+                if (tid == 0) sm.floor_in = mx;
+            }
+            __syncthreads();
+            // one thread per rank: while the rank sends more experts than that, relay its expert with the most
+            // replicas (ties: lower index); a relayed expert leaves its master's rank once instead of reps times
+            for (int r = tid; r < N; r += blockDim.x) {
+                int out = sm.rank_out[r];
+                while (out > sm.floor_in) {
+                    int best = -1, best_reps = 1;
+                    for (int m = 0; m < M; ++m) {
+                        const int l = r * M + m;
+                        if (sm.relay_of[l]) continue;
+                        int reps = plan0.lcnts[l] - 1;
+                        reps = reps > D - 1 ? D - 1 : reps;
+                        if (reps > best_reps && reps <= kMaxRelayReplicas) {
+                            best = l;
+                            best_reps = reps;
+                        }
+                    }
+                    if (best < 0) break;
+                    sm.relay_of[best] = static_cast<unsigned char>(best_reps);
+                    out -= best_reps - 1;
+                }
+            }
+        }
+        __syncthreads();
+    }
     // (the scan below synchronises the CTA before the tables are read)
 
     // blocked scan over (hosted rank, master): active index and replica offsets
@@ -270,8 +333,8 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             const int ai = a_off + a_incl - 1;
             const int rs = r_off + r_incl - reps;
             sm.rep_start[ai] = static_cast<short>(rs);
-            if (kRelay) sm.relay_r[ai] = relayed(reps, relay_min) ? static_cast<unsigned char>(reps) : 0;
             const int l = me * M + m;
+            if (kRelay) sm.relay_r[ai] = sm.relay_of[l];
             auto place = [&](int j, int phys) {
                 const int drank = phys / Lp, dslot = phys % Lp - M;
                 if (phys < 0 || drank >= N || dslot < 0 || dslot >= R) {  // never store outside a slot table
@@ -315,7 +378,19 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         }
         __syncthreads();
     }
-    if (tid == 0) sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxSends ? sm.total_reps : kMaxSends);
+    if (tid == 0) {
+        sm.rep_start[sm.n_active] = static_cast<short>(sm.total_reps < kMaxSends ? sm.total_reps : kMaxSends);
+        if (kRelay) {  // hand-out order: relayed masters first (their chunks have a second hop behind them)
+            int k = 0;
+            for (int a = 0; a < sm.n_active; ++a) {
+                if (sm.relay_r[a]) sm.order[k++] = static_cast<short>(a);
+            }
+            sm.n_relay = k;
+            for (int a = 0; a < sm.n_active; ++a) {
+                if (!sm.relay_r[a]) sm.order[k++] = static_cast<short>(a);
+            }
+        }
+    }
     // Owners of the local replica slots: who sends to this rank; and, for relayed experts, what this
     // rank forwards. One thread per (hosted rank, slot).
     int my_fwd_r = 0, my_fwd_k = -1, my_l = -1;
@@ -326,9 +401,9 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         if (l >= 0) {
             const int src = l / M;
             if (src >= 0 && src < N && src != me) atomicOr(&sm.recv_mask[lr][src >> 5], 1u << (src & 31));
-            if (kRelay && relay_min > 0 && i == tid && l < N * M) {  // nlocal * R <= kMaxFwd <= blockDim.x: one pass
-                const int reps = min(max(call.plan[lr].lcnts[l] - 1, 0), D - 1);
-                if (relayed(reps, relay_min)) {
+            if (kRelay && relay_on && i == tid && l < N * M) {  // nlocal * R <= kMaxFwd <= blockDim.x: one pass
+                const int reps = sm.relay_of[l];
+                if (reps > 0) {
                     const int mine = me * Lp + M + slot;
                     for (int j = 0; j < reps; ++j) {
                         if (call.plan[lr].l2p[static_cast<int64_t>(l) * D + 1 + j] == mine) my_fwd_k = j;
@@ -341,7 +416,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             }
         }
     }
-    if (kRelay && relay_min > 0) {
+    if (kRelay && relay_on) {
         // compact the forward entries (thread order = slot order) and lay out their destination lists
         const unsigned has = __ballot_sync(kFullMask, my_fwd_r > 0);
         const int lane = tid & 31, warp = tid >> 5;
@@ -358,22 +433,22 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             sm.fwd_r[f] = static_cast<unsigned char>(my_fwd_r);
             sm.fwd_k[f] = static_cast<unsigned char>(my_fwd_k);
             sm.fwd_lr[f] = static_cast<unsigned char>(lr);
-            // tiles k, k + r, k + 2r, ... of the expert
-            sm.fwd_tile_start[f + 1] = tiles_per_expert > my_fwd_k ? (tiles_per_expert - my_fwd_k + my_fwd_r - 1) / my_fwd_r : 0;
+            // chunks k, k + r, k + 2r, ... of the expert
+            sm.fwd_unit_start[f + 1] = chunks_per_expert > my_fwd_k ? (chunks_per_expert - my_fwd_k + my_fwd_r - 1) / my_fwd_r : 0;
             sm.fwd_dst_start[f + 1] = static_cast<short>(my_fwd_r - 1);
         }
         __syncthreads();
         if (tid == 0) {
             int nf = 0;
             for (int w = 0; w < kSyncThreads / 32; ++w) nf += sm.w_a[w];
-            sm.fwd_tile_start[0] = 0;
+            sm.fwd_unit_start[0] = 0;
             sm.fwd_dst_start[0] = 0;
             for (int e = 0; e < nf; ++e) {
-                sm.fwd_tile_start[e + 1] += sm.fwd_tile_start[e];
+                sm.fwd_unit_start[e + 1] += sm.fwd_unit_start[e];
                 sm.fwd_dst_start[e + 1] = static_cast<short>(sm.fwd_dst_start[e + 1] + sm.fwd_dst_start[e]);
             }
             sm.n_fwd = nf;
-            sm.fwd_tiles = sm.fwd_tile_start[nf];
+            sm.fwd_units = sm.fwd_unit_start[nf];
         }
         __syncthreads();
         if (my_fwd_r > 0) {
@@ -402,132 +477,186 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
 
     stamp(1);
     // ---- copy -------------------------------------------------------------------------
-    const int send_tiles = sm.n_active * tiles_per_expert;
-    const int total_tiles = send_tiles + sm.fwd_tiles;
+    const int n_relay = kRelay ? sm.n_relay : 0;
+    const int n_direct = sm.n_active - n_relay;
+    const int relay_units = n_relay * chunks_per_expert;
+    const int send_units = relay_units + n_direct * tiles_per_expert;
+    const int total_units = send_units + (kRelay ? sm.fwd_units : 0);
     const uint64_t epoch = sm.epoch;
     DeviceStatus* status0 = call.rank[0]->status;
-    // Tiles are handed out by an atomic counter: CTAs that run on busy SMs (the reroute and the
-    // model's own kernels run next to this one) simply take fewer, and replica counts that differ
+    // Work is handed out by an atomic counter: CTAs that run on busy SMs (the reroute and the
+    // model's own kernels run next to this one) simply take less, and replica counts that differ
     // between masters cannot leave some CTAs with several times the work of others.
-    int* tile_counter = call.rank[0]->sync_ticket + 1;
+    int* unit_counter = call.rank[0]->sync_ticket + 1;
 
-    // Source of a tile. A forward tile first waits (bounded) until the master has delivered it here.
-    auto tile_source = [&](const TileRef& t, bool& ok) -> const uint8_t* {
-        if (!kRelay || t.active >= 0) return sm.src[t.active][t.shard] + t.offset;
-        const int f = -1 - t.active;
-        if (!wait_flag_ge_relaxed(sm.fwd_flags[f] + t.tile_in_expert, epoch, call.timeout_ns)) {
+    auto decode_unit = [&](int u) -> Unit {
+        Unit un;
+        if (kRelay && u < relay_units) {
+            const int nr = kRelay ? n_relay : 1;  // (never zero where this branch can run)
+            un.kind = 1;
+            un.who = sm.order[u % nr];
+            un.chunk = u / nr;
+            un.tile = un.chunk * kChunkTiles;
+            un.tile_end = min(un.tile + kChunkTiles, tiles_per_expert);
+        } else if (!kRelay || u < send_units) {
+            const int v = u - relay_units;
+            un.kind = 0;
+            un.who = kRelay ? sm.order[n_relay + v % n_direct] : v % n_direct;
+            un.chunk = 0;
+            un.tile = v / n_direct;
+            un.tile_end = un.tile + 1;
+        } else {
+            const int v = u - send_units;
+            int f = 0;
+            while (f + 1 < sm.n_fwd && v >= sm.fwd_unit_start[f + 1]) ++f;
+            un.kind = 2;
+            un.who = f;
+            un.chunk = sm.fwd_k[f] + (v - sm.fwd_unit_start[f]) * sm.fwd_r[f];
+            un.tile = un.chunk * kChunkTiles;
+            un.tile_end = min(un.tile + kChunkTiles, tiles_per_expert);
+        }
+        return un;
+    };
+    // Source of a tile (a forwarded tile is read from the local slot it landed in).
+    auto tile_source = [&](const TileRef& t) -> const uint8_t* {
+        if (!kRelay || t.kind != 2) return sm.src[t.who][t.shard] + t.offset;
+        return shard_base(sm.fwd_src_w[t.who], sm.fwd_src_s[t.who], sh, t.shard) + t.offset;
+    };
+    // A forwarded chunk may be read once the master has delivered it here: bounded wait on its ready flag.
+    auto wait_chunk = [&](const Unit& un) -> bool {
+        bool ok = true;
+        if (!wait_flag_ge_relaxed(sm.fwd_flags[un.who] + un.chunk, epoch, call.timeout_ns)) {
             ok = false;
-            report_error(call.rank[sm.fwd_lr[f]]->status, UEP_DEV_TIMEOUT_SYNC, t.tile_in_expert);
+            report_error(call.rank[sm.fwd_lr[un.who]]->status, UEP_DEV_TIMEOUT_SYNC, un.chunk);
         }
         __threadfence_system();        // acquire side of the flag
-        fence_proxy_async_global();    // ... also for the bulk copy that reads the tile next
-        return shard_base(sm.fwd_src_w[f], sm.fwd_src_s[f], sh, t.shard) + t.offset;
+        fence_proxy_async_global();    // ... also for the bulk copies that read the chunk next
+        return ok;
     };
-    // Destinations of a tile: d = 0 .. count-1 -> address (null: skip). For a relayed send tile the single
-    // destination is replica (tile mod r), and `flag` is that replica's ready flag for the tile.
-    auto dest_range = [&](const TileRef& t, int& first, int& count, uint64_t*& flag) {
-        flag = nullptr;
-        if (t.active >= 0) {
-            const int r0 = sm.rep_start[t.active], r1 = sm.rep_start[t.active + 1];
-            const int rr = kRelay ? sm.relay_r[t.active] : 0;
-            if (rr == 0) {
+    // Destinations of a tile: d = first .. first+count-1 -> address (null: skip). A scattered chunk has one
+    // destination, replica (chunk mod r).
+    auto dest_range = [&](const TileRef& t, int& first, int& count) {
+        if (!kRelay || t.kind != 2) {
+            const int r0 = sm.rep_start[t.who], r1 = sm.rep_start[t.who + 1];
+            if (!kRelay || t.kind == 0) {
                 first = r0;
                 count = r1 - r0;
             } else {
-                first = r0 + t.tile_in_expert % rr;
+                first = r0 + t.chunk % sm.relay_r[t.who];
                 count = first < r1 ? 1 : 0;
-                if (count && sm.dst_flags[first] != nullptr) flag = sm.dst_flags[first] + t.tile_in_expert;
             }
         } else {
-            const int f = -1 - t.active;
-            first = sm.fwd_dst_start[f];
-            count = sm.fwd_dst_start[f + 1] - first;
+            first = sm.fwd_dst_start[t.who];
+            count = sm.fwd_dst_start[t.who + 1] - first;
         }
     };
     auto dest_addr = [&](const TileRef& t, int d) -> uint8_t* {
-        uint8_t* w = (!kRelay || t.active >= 0) ? sm.dst_weight[d] : sm.fwd_dst_w[d];
+        uint8_t* w = (!kRelay || t.kind != 2) ? sm.dst_weight[d] : sm.fwd_dst_w[d];
         if (w == nullptr) return nullptr;
-        uint8_t* s = (!kRelay || t.active >= 0) ? sm.dst_scale[d] : sm.fwd_dst_s[d];
+        uint8_t* s = (!kRelay || t.kind != 2) ? sm.dst_scale[d] : sm.fwd_dst_s[d];
         return shard_base(w, s, sh, t.shard) + t.offset;
+    };
+    // Ready flag of a scattered chunk on the replica that receives it (null: nothing to raise).
+    auto chunk_flag = [&](const Unit& un) -> uint64_t* {
+        const int r0 = sm.rep_start[un.who], r1 = sm.rep_start[un.who + 1];
+        const int d = r0 + un.chunk % sm.relay_r[un.who];
+        if (d >= r1 || sm.dst_flags[d] == nullptr) return nullptr;
+        return sm.dst_flags[d] + un.chunk;
     };
 
     if (sm.all_aligned) {
         if (tid == 0) {
-            int ring_tile[kSyncStages];        // tile index held by each stage (>= total_tiles: none)
-            uint64_t* flag_ring[kSyncStages];  // ready flag owed for the k-th stored tile, slot k % stages
+            TileRef ring[kSyncStages];         // the tile held by each stage
+            bool ring_valid[kSyncStages];
+            uint64_t* ring_flag[kSyncStages];  // ready flag to raise once that stage's tile is stored (last tile of a chunk)
+            uint64_t* owed[kSyncStages];       // ready flag owed for the k-th stored tile, slot k % stages
             uint32_t phase_bits = 0;           // bit s: parity the next wait on stage s expects
             bool ok = true;
-            // The index of the next tile is requested one load ahead, so the round trip of the
+            // The index of the next unit is requested one load ahead, so the round trip of the
             // atomic overlaps with the copies instead of sitting in front of every load.
-            int pending = atomicAdd(tile_counter, 1);
+            int pending = atomicAdd(unit_counter, 1);
+            Unit cur{};
+            int cur_tile = 0;
+            bool have_cur = false;
 #pragma unroll
-            for (int s = 0; s < kSyncStages; ++s) flag_ring[s] = nullptr;
-            // Two passes over the same ring: first the send tiles, then the forward tiles. A CTA must
+            for (int s = 0; s < kSyncStages; ++s) owed[s] = nullptr;
+            // Two passes over the same ring: first the send units, then the forward units. A CTA must
             // not wait for a ready flag while it still holds send tiles it has loaded but not stored,
             // or ready flags it has not raised: another CTA (here or on a peer) may be waiting for
-            // exactly those. So the first pass stops at the first forward tile, drains, raises its
+            // exactly those. So the first pass stops at the first forward unit, drains, raises its
             // flags, and only the second pass waits.
             for (int pass = 0; pass < (kRelay ? 2 : 1); ++pass) {
-                const int limit = pass == 0 ? send_tiles : total_tiles;
-                if (pending >= limit) continue;
+                const int limit = pass == 0 ? send_units : total_units;
+                if (pending >= limit && !have_cur) continue;
                 auto issue_load = [&](int s) {
-                    const int idx = pending;
-                    ring_tile[s] = idx < limit ? idx : total_tiles;
-                    if (idx >= limit) return;  // keeps `pending`: a claimed forward tile waits for the second pass
-                    pending = atomicAdd(tile_counter, 1);
-                    const TileRef t = decode_tile<kSyncTile, kRelay>(idx, send_tiles, sm, sh);
-                    const uint8_t* src = tile_source(t, ok);
+                    ring_valid[s] = false;
+                    if (!have_cur || cur_tile >= cur.tile_end) {
+                        have_cur = false;
+                        if (pending >= limit) return;  // keeps `pending`: a claimed forward unit waits for the second pass
+                        cur = decode_unit(pending);
+                        cur_tile = cur.tile;
+                        have_cur = true;
+                        pending = atomicAdd(unit_counter, 1);
+                        if (kRelay && cur.kind == 2 && !wait_chunk(cur)) ok = false;
+                    }
+                    TileRef t;
+                    t.kind = cur.kind;
+                    t.who = cur.who;
+                    t.chunk = cur.chunk;
+                    t.tile_in_expert = cur_tile;
+                    locate_tile<kSyncTile>(t, sh, shard_tiles);
+                    ++cur_tile;
+                    ring[s] = t;
+                    ring_valid[s] = true;
+                    ring_flag[s] = (kRelay && cur.kind == 1 && cur_tile == cur.tile_end) ? chunk_flag(cur) : nullptr;
                     const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
                     if (bytes16) {
                         mbar_expect_tx(&bars[s], bytes16);
-                        bulk_load(smem_raw + s * kSyncTile, src, bytes16, &bars[s]);
+                        bulk_load(smem_raw + s * kSyncTile, tile_source(t), bytes16, &bars[s]);
                     }
                 };
 #pragma unroll
-                for (int s = 0; s < kSyncStages; ++s) ring_tile[s] = total_tiles;
+                for (int s = 0; s < kSyncStages; ++s) ring_valid[s] = false;
 #pragma unroll
                 for (int s = 0; s < kSyncStages - 1; ++s) issue_load(s);
                 int k = 0;
                 while (true) {
                     const int s = k % kSyncStages;
-                    const int idx = ring_tile[s];
-                    if (idx >= total_tiles) break;  // indices are handed out in order: nothing is left for this pass
-                    const TileRef t = decode_tile<kSyncTile, kRelay>(idx, send_tiles, sm, sh);
+                    if (!ring_valid[s]) break;  // units are handed out in order: nothing is left for this pass
+                    const TileRef t = ring[s];
                     const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
                     if (bytes16) {
                         if (!mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns)) {
                             ok = false;
                             report_error(status0, UEP_DEV_TIMEOUT_COPY, k);
-                            ring_tile[s] = total_tiles;
-                            break;
+                            break;  // the stage stays marked valid: its load is waited for below
                         }
                         phase_bits ^= 1u << s;
                     }
-                    ring_tile[s] = total_tiles;
+                    ring_valid[s] = false;
                     int first, count;
-                    uint64_t* flag;
-                    dest_range(t, first, count, flag);
+                    dest_range(t, first, count);
                     for (int d = first; d < first + count; ++d) {
                         uint8_t* dst = dest_addr(t, d);
                         if (dst == nullptr) continue;
                         if (bytes16) bulk_store(dst, smem_raw + s * kSyncTile, bytes16);
                         if (static_cast<uint32_t>(t.bytes) != bytes16) {  // up to 15 trailing bytes of a shard
-                            const uint8_t* src =
-                                (!kRelay || t.active >= 0) ? sm.src[t.active][t.shard] + t.offset
-                                              : shard_base(sm.fwd_src_w[-1 - t.active], sm.fwd_src_s[-1 - t.active], sh, t.shard) + t.offset;
+                            const uint8_t* src = tile_source(t);
                             for (int b = bytes16; b < t.bytes; ++b) dst[b] = __ldcg(src + b);
                         }
                     }
                     bulk_commit();
-                    // A relayed tile's ready flag may go out once its stores are complete, not merely read:
-                    // the flag of the tile stored kSyncStages-1 iterations ago is due now.
+                    // A chunk's ready flag may go out once its stores are complete, not merely read: the flag
+                    // owed for the tile stored kSyncStages-1 iterations ago is due now (groups complete in order,
+                    // so the earlier tiles of that chunk are complete as well).
                     if (kRelay) {
-                        uint64_t* due = flag_ring[(k + 1) % kSyncStages];
-                        flag_ring[(k + 1) % kSyncStages] = nullptr;
-                        flag_ring[s] = flag;
+                        uint64_t* due = owed[(k + 1) % kSyncStages];
+                        owed[(k + 1) % kSyncStages] = nullptr;
+                        owed[s] = ring_flag[s];
                         if (due != nullptr) {
                             bulk_wait_all<kSyncStages - 1>();
-                            st_release_sys_u64(due, epoch);
+                            __threadfence_system();
+                            st_relaxed_sys_u64(due, epoch);
                         }
                     }
                     // refill the stage that the previous tile's stores have finished reading
@@ -541,20 +670,22 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                 bool any_flag = false;
                 if (kRelay) {
 #pragma unroll
-                    for (int s = 0; s < kSyncStages; ++s) any_flag |= flag_ring[s] != nullptr;
+                    for (int s = 0; s < kSyncStages; ++s) any_flag |= owed[s] != nullptr;
                 }
                 if (any_flag) {
                     __threadfence_system();
 #pragma unroll
                     for (int s = 0; s < kSyncStages; ++s) {
-                        if (flag_ring[s] != nullptr) st_relaxed_sys_u64(flag_ring[s], epoch);
-                        flag_ring[s] = nullptr;
+                        if (owed[s] != nullptr) st_relaxed_sys_u64(owed[s], epoch);
+                        owed[s] = nullptr;
                     }
                 }
                 if (!ok) {
                     // loads still in flight must land before the shared memory is released or reused
                     for (int s = 0; s < kSyncStages; ++s) {
-                        if (ring_tile[s] < total_tiles) mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns);
+                        if (ring_valid[s] && (static_cast<uint32_t>(ring[s].bytes) & ~15u)) {
+                            mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns);
+                        }
                     }
                     break;
                 }
@@ -564,39 +695,42 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     } else {
         while (true) {
             __syncthreads();
-            if (tid == 0) sm.s_tile = atomicAdd(tile_counter, 1);
+            if (tid == 0) sm.s_unit = atomicAdd(unit_counter, 1);
             __syncthreads();
-            const int idx = sm.s_tile;
-            if (idx >= total_tiles) break;
-            const TileRef t = decode_tile<kSyncTile, kRelay>(idx, send_tiles, sm, sh);
-            if (kRelay && t.active < 0) {  // forward tile: one thread waits for the master's delivery
-                if (tid == 0) {
-                    bool ok = true;
-                    (void)tile_source(t, ok);
-                }
+            const int u = sm.s_unit;
+            if (u >= total_units) break;
+            const Unit un = decode_unit(u);
+            if (kRelay && un.kind == 2) {  // forward chunk: one thread waits for the master's delivery
+                if (tid == 0) (void)wait_chunk(un);
                 __syncthreads();
             }
-            const uint8_t* src = (!kRelay || t.active >= 0)
-                                     ? sm.src[t.active][t.shard] + t.offset
-                                     : shard_base(sm.fwd_src_w[-1 - t.active], sm.fwd_src_s[-1 - t.active], sh, t.shard) + t.offset;
-            int first, count;
-            uint64_t* flag;
-            dest_range(t, first, count, flag);
-            for (int d = first; d < first + count; ++d) {
-                uint8_t* dst = dest_addr(t, d);
-                if (dst != nullptr) copy_plain(src, dst, t.bytes, !kRelay || t.active >= 0);
+            for (int tile = un.tile; tile < un.tile_end; ++tile) {
+                TileRef t;
+                t.kind = un.kind;
+                t.who = un.who;
+                t.chunk = un.chunk;
+                t.tile_in_expert = tile;
+                locate_tile<kSyncTile>(t, sh, shard_tiles);
+                const uint8_t* src = tile_source(t);
+                int first, count;
+                dest_range(t, first, count);
+                for (int d = first; d < first + count; ++d) {
+                    uint8_t* dst = dest_addr(t, d);
+                    if (dst != nullptr) copy_plain(src, dst, t.bytes, !kRelay || t.kind != 2);
+                }
             }
-            if (flag != nullptr) {  // every thread's stores, then the flag
+            if (kRelay && un.kind == 1) {  // every thread's stores, then the chunk's flag
+                uint64_t* flag = chunk_flag(un);
                 __threadfence_system();
                 __syncthreads();
-                if (tid == 0) st_release_sys_u64(flag, epoch);
+                if (tid == 0 && flag != nullptr) st_relaxed_sys_u64(flag, epoch);
             }
         }
     }
     // Order this CTA's copies before its ticket. On the bulk-copy path only thread 0 issued
     // copies and it has already waited for their completion.
     // Device scope is enough here: the ticket below hands these writes to the last CTA, whose
-    // system-scope release of the flags then covers them (causality is transitive across scopes).
+    // system-scope fence in front of the flags then covers them (causality is transitive across scopes).
     if (!sm.all_aligned || tid == 0) __threadfence();
     __syncthreads();
     stamp(4);
@@ -609,7 +743,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         if (ticket == static_cast<int>(gridDim.x) - 1) {
             __threadfence();  // the other CTAs' copies, fenced before their tickets, are ordered before the flags
             *ticket_ptr = 0;
-            *tile_counter = 0;  // every CTA has stopped taking tiles
+            *unit_counter = 0;  // every CTA has stopped taking work
             sm.is_last = 1;
             *call.sync_epoch = epoch;  // this launch's epoch is closed
         }
@@ -713,7 +847,7 @@ cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         attr_set_for[relay] = fn;
     }
-    // Hosted ranks pool their tiles over all CTAs. Without relaying, the only waits are those of the
+    // Hosted ranks pool their work over all CTAs. Without relaying, the only waits are those of the
     // last CTA, on flags that peers on other devices write. With relaying, CTAs that forward wait for
     // CTAs that send; when both are in this launch (ranks hosted together) they must be co-resident,
     // which a cooperative launch guarantees.

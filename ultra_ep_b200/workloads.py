@@ -159,3 +159,75 @@ def expert_weight_bytes(cfg: LayerConfig, global_expert: int, shard: int, nbytes
 def fp32_grads(seed_key, numel: int, std: float) -> np.ndarray:
     rng = np.random.default_rng(seed_key)
     return rng.normal(0.0, std, numel).astype(np.float32)
+
+
+# ------------------------------------------------------------------------------------------
+# The skew model of the reference's own test scripts (tests/utils.py:355-561 of the reference),
+# restated on numpy: expert popularity = (rank weight ~ rank^-alpha) x (position weight ~ position^-4
+# inside the rank), with alpha found by bisection so that the expected max/mean rank load, under top-k
+# sampling WITHOUT replacement, meets a target ratio. Draws use numpy's generator (Gumbel top-k), so the
+# tokens differ from the reference's torch.multinomial draws while following the same distribution.
+# ------------------------------------------------------------------------------------------
+def _topk_inclusion_probs(weights: np.ndarray, topk: int) -> np.ndarray:
+    """Approximate probability that each expert is among the k drawn: 1 - exp(-c w) with sum = k."""
+    w = weights.astype(np.float64)
+    lo, hi = 0.0, 1.0
+    while float((1.0 - np.exp(-hi * w)).sum()) < topk:
+        hi *= 2.0
+    for _ in range(48):
+        mid = (lo + hi) * 0.5
+        if float((1.0 - np.exp(-mid * w)).sum()) < topk:
+            lo = mid
+        else:
+            hi = mid
+    return 1.0 - np.exp(-hi * w)
+
+
+def _rank_skew_weights(num_ranks: int, masters: int, rank_alpha: float, local_alpha: float) -> np.ndarray:
+    rw = 1.0 / np.arange(1, num_ranks + 1, dtype=np.float64) ** rank_alpha
+    lw = 1.0 / np.arange(1, masters + 1, dtype=np.float64) ** local_alpha
+    w = (rw[:, None] * lw[None, :]).reshape(-1)
+    return (w / w.sum()).astype(np.float32)
+
+
+def rank_skew_popularity(num_ranks: int, masters: int, topk: int, imbalance_ratio: float) -> np.ndarray:
+    """Expert popularity whose expected max/mean rank load is `imbalance_ratio` (>= 1)."""
+    L = num_ranks * masters
+    if imbalance_ratio <= 1.0:
+        return np.full(L, 1.0 / L, np.float32)
+    local_alpha = 4.0 if masters > 1 else 0.0
+
+    def ratio(alpha: float) -> float:
+        w = _rank_skew_weights(num_ranks, masters, alpha, local_alpha)
+        loads = _topk_inclusion_probs(w, topk).reshape(num_ranks, masters).sum(1)
+        return float(loads.max() / loads.mean())
+
+    lo, hi = 0.0, 8.0
+    for _ in range(32):
+        mid = (lo + hi) * 0.5
+        if ratio(mid) < imbalance_ratio:
+            lo = mid
+        else:
+            hi = mid
+    return _rank_skew_weights(num_ranks, masters, hi, local_alpha)
+
+
+def reference_style_loads(num_ranks: int, masters: int, topk: int, tokens_per_rank: int, imbalance_ratio: float,
+                          seed: int = 33):
+    """(int32 [N, L] per-rank loads, int32 [T, K] routing ids of rank 0) under the skew model above."""
+    L = num_ranks * masters
+    p = rank_skew_popularity(num_ranks, masters, topk, imbalance_ratio).astype(np.float64)
+    logp = np.log(p / p.sum())
+    rows, ids0 = [], None
+    for r in range(num_ranks):
+        rng = np.random.default_rng(seed + r * 104729)
+        u = rng.random((tokens_per_rank, L), dtype=np.float32)
+        np.maximum(u, np.float32(1e-30), out=u)
+        keys = logp.astype(np.float32)[None, :] - np.log(-np.log(u))  # Gumbel top-k = sampling without replacement
+        part = np.argpartition(-keys, topk - 1, axis=1)[:, :topk]
+        order = np.argsort(-np.take_along_axis(keys, part, axis=1), axis=1, kind="stable")
+        ids = np.take_along_axis(part, order, axis=1).astype(np.int32)
+        if r == 0:
+            ids0 = ids
+        rows.append(np.bincount(ids.reshape(-1), minlength=L))
+    return np.stack(rows).astype(np.int32), ids0
