@@ -205,7 +205,8 @@ constexpr int kDenseMaxChunkCols = 512;
 __host__ __device__ __forceinline__ int dense_row_stride(int L) { return (L + 15) / 16 * 16 + 16; }
 
 __global__ void __launch_bounds__(kRerouteThreads)
-dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_mode, int interleave, int chunk_cols) {
+dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_mode, int interleave, int chunk_cols,
+                     int overlapped) {
     const DenseFwdArgs& a = batch.a[blockIdx.y];
     const uint8_t* __restrict__ map = a.map;
     const float* __restrict__ probs = a.probs;
@@ -272,24 +273,9 @@ dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_m
     }
     zero_tile(min(chunk_cols, P));
     __syncthreads();
-    // one thread per expert walks its column only to count: a routed cell of an expert with several instances
-    // is marked 0x80 | (its rank among the tile's routed rows, < 64); with one instance the choice is 0 at once
-    for (int e = tid; e < L; e += blockDim.x) {
-        const int C = routers[e].C;
-        int seen = 0;
-        for (int t = 0; t < rows; ++t) {
-            uint8_t c = 0xFF;
-            if (choice[t * Ls + e]) {
-                c = C <= 1 ? 0 : static_cast<uint8_t>(0x80 | seen);
-                ++seen;
-            }
-            choice[t * Ls + e] = c;
-        }
-    }
-
     // ---- ordinal base of every expert: tokens routed to it in the tiles in front of this one ---
-    pdl_wait();
     const uint8_t* counts = reinterpret_cast<const uint8_t*>(a.scratch);
+    auto sum_earlier_tiles = [&]() {
     if (dense_fast_path(map, a.scratch, L)) {
         const int G = L / 16;
         const int g = tid % G, sub = tid / G, nsub = blockDim.x / G;
@@ -354,6 +340,29 @@ dense_scatter_kernel(Batch<DenseFwdArgs> batch, int L, int P, int D, int quota_m
             for (int tl = 0; tl < tile; ++tl) b += __ldcg(counts + static_cast<int64_t>(tl) * L + e);
             base_of[e] = b;
         }
+    }
+    };
+    // Launched behind the count kernel in the ordinary way, its counts are complete already and their loads go out
+    // before the column walk; launched as a dependent kernel, everything up to the wait reads the map and the plan only.
+    if (!overlapped) sum_earlier_tiles();
+    // one thread per expert walks its column only to count: a routed cell of an expert with several instances
+    // is marked 0x80 | (its rank among the tile's routed rows, < 64); with one instance the choice is 0 at once
+    for (int e = tid; e < L; e += blockDim.x) {
+        const int C = routers[e].C;
+        int seen = 0;
+        for (int t = 0; t < rows; ++t) {
+            uint8_t c = 0xFF;
+            if (choice[t * Ls + e]) {
+                c = C <= 1 ? 0 : static_cast<uint8_t>(0x80 | seen);
+                ++seen;
+            }
+            choice[t * Ls + e] = c;
+        }
+    }
+
+    if (overlapped) {
+        pdl_wait();
+        sum_earlier_tiles();
     }
     __syncthreads();
 
@@ -588,7 +597,7 @@ __global__ void __launch_bounds__(kRerouteThreads) sparse_count_kernel(Batch<Spa
 
 template <typename IdT>
 __global__ void __launch_bounds__(kRerouteThreads)
-sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interleave) {
+sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interleave, int overlapped) {
     extern __shared__ __align__(128) char smem_raw[];
     const SparseArgs& a = batch.a[blockIdx.y];
     const IdT* ids = static_cast<const IdT*>(a.ids);
@@ -606,19 +615,27 @@ sparse_reroute_kernel(Batch<SparseArgs> batch, int K, int L, int D, int interlea
     int32_t* l2p_s = prefix_s + static_cast<size_t>(L) * kStagedReps;
     int32_t* warp_base = l2p_s + static_cast<size_t>(L) * kStagedReps;
     const int tile = blockIdx.x;
-    // prologue (plan and ids only): routing parameters, staged plan rows and the per-warp counts of this tile
+    auto sum_earlier_tiles = [&]() {
+        for (int e = threadIdx.x; e < L; e += blockDim.x) {
+            int b = 0;
+#pragma unroll 8
+            for (int tl = 0; tl < tile; ++tl) b += __ldcg(tile_counts + static_cast<int64_t>(tl) * L + e);
+            base[e] = b;
+        }
+    };
+    // Launched behind the count kernel in the ordinary way, its counts are complete already: their loads go out
+    // together with those of the plan rows. Launched as a dependent kernel, everything up to the wait reads the
+    // plan and the ids only.
+    if (!overlapped) sum_earlier_tiles();
     for (int e = threadIdx.x; e < L; e += blockDim.x) {
         stage_expert(e, lcnts, rqp, l2p, D, interleave != 2, interleave == 1, routers, prefix_s, l2p_s);  // 2: round-robin (legacy placement)
     }
     tile_warp_counts<IdT>(ids, n, L, false, warp_base);
-    pdl_wait();  // the tile counts of the first kernel are complete from here on
-    for (int e = threadIdx.x; e < L; e += blockDim.x) {
-        int b = 0;
-#pragma unroll 8
-        for (int tl = 0; tl < tile; ++tl) b += __ldcg(tile_counts + static_cast<int64_t>(tl) * L + e);
-        base[e] = b;
+    if (overlapped) {
+        pdl_wait();  // the tile counts of the first kernel are complete from here on
+        sum_earlier_tiles();
+        __syncthreads();
     }
-    __syncthreads();
     // ids may alias out: every entry is read and written by the same lane, the write comes
     // last, and tiles do not overlap.
     tile_resolve<IdT>(ids, n, L, false, base, warp_base, [&](int64_t i, int b, int ordinal) {
@@ -780,8 +797,9 @@ __global__ void __launch_bounds__(256) gather_rows_plain_kernel(const uint8_t* _
 }
 
 cudaError_t ensure_smem_attr(const void* fn, size_t bytes) {
-    if (bytes <= 48 * 1024) return cudaSuccess;
-    // remembered per kernel: the attribute is set again only when a launch needs more than any before it
+    // Remembered per kernel. On first use the kernel also asks for the largest shared-memory carve-out: these
+    // kernels run next to weight_sync, whose CTAs need most of an SM's shared memory, and an SM that was set up
+    // with a small carve-out for a reroute CTA cannot take a weight_sync CTA until it has drained.
     static std::mutex mu;
     static const void* fns[16];
     static size_t granted[16];
@@ -789,10 +807,18 @@ cudaError_t ensure_smem_attr(const void* fn, size_t bytes) {
     std::lock_guard<std::mutex> lock(mu);
     int i = 0;
     while (i < n && fns[i] != fn) ++i;
-    if (i < n && granted[i] >= bytes) return cudaSuccess;
+    if (i == n) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        if (n < 16) {
+            fns[n] = fn;
+            granted[n] = 48 * 1024;
+            ++n;
+        }
+    }
+    if (bytes <= 48 * 1024 || (i < 16 && granted[i] >= bytes)) return cudaSuccess;
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
     if (e != cudaSuccess) return e;
-    if (i == n && n < 16) fns[n++] = fn;
     if (i < 16) granted[i] = bytes;
     return cudaSuccess;
 }
@@ -808,13 +834,18 @@ int64_t sparse_scratch_elems(int64_t entries, int L) { return sparse_tiles(entri
 // Launch of a kernel that may start before the kernel in front of it in the stream has finished
 // (programmatic dependent launch); the kernel calls pdl_wait() before it reads that kernel's output.
 // UEP_DISABLE_PDL=1 turns the attribute off (the pair then runs strictly one after the other).
-template <typename... Params, typename... Args>
-cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args&&... args) {
+bool pdl_enabled() {
     static const bool disabled = [] {
         const char* e = std::getenv("UEP_DISABLE_PDL");
         return e != nullptr && e[0] == '1';
     }();
+    return !disabled;
+}
+
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             bool overlap, Args&&... args) {
+    const bool disabled = !pdl_enabled();
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -824,7 +855,7 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = disabled ? 0 : 1;
+    cfg.numAttrs = (disabled || !overlap) ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
@@ -854,8 +885,11 @@ cudaError_t launch_dense_forward(const Batch<DenseFwdArgs>& b, int L, int P, int
     dense_count_kernel<<<grid, kRerouteThreads, smem_count, stream>>>(b, L);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return launch_dependent(dense_scatter_kernel, grid, dim3(kRerouteThreads), smem, stream, b, L, P, D, quota_mode,
-                            interleave, chunk);
+    // With one rank per launch the pair is latency-bound and the overlap pays; a launch that hosts several ranks
+    // fills the device with the first kernel alone, and early CTAs of the second only get in its way.
+    const bool overlap = b.n == 1 && pdl_enabled();
+    return launch_dependent(dense_scatter_kernel, grid, dim3(kRerouteThreads), smem, stream, overlap, b, L, P, D, quota_mode,
+                            interleave, chunk, overlap ? 1 : 0);
 }
 
 cudaError_t launch_dense_backward(const Batch<DenseBwdArgs>& b, int L, int P, int D, cudaStream_t stream) {
@@ -892,7 +926,9 @@ static cudaError_t launch_sparse_typed(const Batch<SparseArgs>& b, int K, int L,
     sparse_count_kernel<IdT><<<grid, kRerouteThreads, smem1, stream>>>(b, K, L);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return launch_dependent(sparse_reroute_kernel<IdT>, grid, dim3(kRerouteThreads), smem2, stream, b, K, L, D, interleave);
+    const bool overlap = b.n == 1 && pdl_enabled();
+    return launch_dependent(sparse_reroute_kernel<IdT>, grid, dim3(kRerouteThreads), smem2, stream, overlap, b, K, L, D, interleave,
+                            overlap ? 1 : 0);
 }
 
 cudaError_t launch_sparse_reroute(const Batch<SparseArgs>& b, int ids_kind, int K, int L, int D, int interleave,
@@ -1043,7 +1079,7 @@ int uep_dispatch_positions(const int32_t* phys_ids, int64_t num_entries, int P, 
     count_launch(2);
     key_count_kernel<int32_t><<<tiles, kRerouteThreads, smem1, stream>>>(phys_ids, num_entries, P, 1, scratch);
     UEP_CUDA_TRY(cudaGetLastError());
-    UEP_CUDA_TRY(launch_dependent(dispatch_positions_kernel, dim3(tiles), dim3(kRerouteThreads), smem2, stream, phys_ids,
+    UEP_CUDA_TRY(launch_dependent(dispatch_positions_kernel, dim3(tiles), dim3(kRerouteThreads), smem2, stream, true, phys_ids,
                                   num_entries, P, static_cast<const int32_t*>(scratch), tiles, pos, expert_offsets));
     return UEP_OK;
 }

@@ -53,6 +53,23 @@ constexpr int kMaxRelayReplicas = 16;
 constexpr int kMaxFwdDst = kMaxFwd * (kMaxRelayReplicas - 1);
 constexpr int kChunkTiles = 4;                    // tiles per relayed chunk (one ready flag per chunk)
 
+// One unit of work as the counter hands it out.
+struct Unit {
+    int kind;            // 0: one tile of a direct expert; 1: a chunk a master scatters; 2: a chunk a replica forwards
+    int who;             // kind 0/1: index of the active master; kind 2: forward entry
+    int tile, tile_end;  // tile range over the expert's shards
+    int chunk;           // kind 1/2: chunk index (selects the ready flag)
+};
+
+struct TileRef {
+    int kind, who;
+    int tile_in_expert;  // tile index over the expert's shards
+    int shard;           // 0..3
+    int64_t offset;      // byte offset inside the shard
+    int bytes;           // bytes of this tile
+    int chunk;
+};
+
 struct SyncShared {
     int n_active;          // masters (of all hosted ranks) that have replicas
     int total_reps;        // sum of their replica counts
@@ -95,23 +112,13 @@ struct SyncShared {
     uint8_t* fwd_dst_w[kMaxFwdDst];
     uint8_t* fwd_dst_s[kMaxFwdDst];
     __align__(8) uint64_t bars[8];
-};
-
-// One unit of work as the counter hands it out.
-struct Unit {
-    int kind;            // 0: one tile of a direct expert; 1: a chunk a master scatters; 2: a chunk a replica forwards
-    int who;             // kind 0/1: index of the active master; kind 2: forward entry
-    int tile, tile_end;  // tile range over the expert's shards
-    int chunk;           // kind 1/2: chunk index (selects the ready flag)
-};
-
-struct TileRef {
-    int kind, who;
-    int tile_in_expert;  // tile index over the expert's shards
-    int shard;           // 0..3
-    int64_t offset;      // byte offset inside the shard
-    int bytes;           // bytes of this tile
-    int chunk;
+    // State of the issuing thread's ring, kept here rather than in its local memory: the kernels that run
+    // next to this one evict the L1 lines a stack frame lives in, and every miss would sit on the critical
+    // path of a tile.
+    TileRef ring[8];         // the tile held by each stage
+    uint64_t* ring_flag[8];  // ready flag to raise once that stage's tile is stored (last tile of a chunk)
+    uint64_t* owed[8];       // ready flag owed for the k-th stored tile, slot k % stages
+    int ring_valid[8];
 };
 
 template <int kSyncTile>
@@ -566,10 +573,10 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
 
     if (sm.all_aligned) {
         if (tid == 0) {
-            TileRef ring[kSyncStages];         // the tile held by each stage
-            bool ring_valid[kSyncStages];
-            uint64_t* ring_flag[kSyncStages];  // ready flag to raise once that stage's tile is stored (last tile of a chunk)
-            uint64_t* owed[kSyncStages];       // ready flag owed for the k-th stored tile, slot k % stages
+            TileRef* ring = sm.ring;
+            int* ring_valid = sm.ring_valid;
+            uint64_t** ring_flag = sm.ring_flag;
+            uint64_t** owed = sm.owed;
             uint32_t phase_bits = 0;           // bit s: parity the next wait on stage s expects
             bool ok = true;
             // The index of the next unit is requested one load ahead, so the round trip of the
@@ -589,7 +596,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                 const int limit = pass == 0 ? send_units : total_units;
                 if (pending >= limit && !have_cur) continue;
                 auto issue_load = [&](int s) {
-                    ring_valid[s] = false;
+                    ring_valid[s] = 0;
                     if (!have_cur || cur_tile >= cur.tile_end) {
                         have_cur = false;
                         if (pending >= limit) return;  // keeps `pending`: a claimed forward unit waits for the second pass
@@ -607,7 +614,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                     locate_tile<kSyncTile>(t, sh, shard_tiles);
                     ++cur_tile;
                     ring[s] = t;
-                    ring_valid[s] = true;
+                    ring_valid[s] = 1;
                     ring_flag[s] = (kRelay && cur.kind == 1 && cur_tile == cur.tile_end) ? chunk_flag(cur) : nullptr;
                     const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
                     if (bytes16) {
@@ -616,7 +623,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                     }
                 };
 #pragma unroll
-                for (int s = 0; s < kSyncStages; ++s) ring_valid[s] = false;
+                for (int s = 0; s < kSyncStages; ++s) ring_valid[s] = 0;
 #pragma unroll
                 for (int s = 0; s < kSyncStages - 1; ++s) issue_load(s);
                 int k = 0;
@@ -633,7 +640,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                         }
                         phase_bits ^= 1u << s;
                     }
-                    ring_valid[s] = false;
+                    ring_valid[s] = 0;
                     int first, count;
                     dest_range(t, first, count);
                     for (int d = first; d < first + count; ++d) {
