@@ -317,7 +317,8 @@ int uep_debug_sync_trace(uep_manager* m, unsigned long long* host_out, int max_c
 
 /* Measurement aid: time of one one-directional copy of `bytes` bytes (a multiple of 16, at most the replica
  * weight buffer) from this rank's replica weight buffer into peer_rank's, averaged over `iters` copies on the
- * communication stream; use_kernel 0: cudaMemcpyAsync (copy engine), 1: a plain load/store kernel. Overwrites
+ * communication stream; use_kernel 0: cudaMemcpyAsync (copy engine), 1: a plain load/store kernel; add 2 to copy
+ * the other way (this rank reads the peer's buffer: the direction of the Wgrad reduce's loads). Overwrites
  * the peer's replica slots; the peer must be idle. Gives the link bandwidth the copy and reduce kernels are
  * measured against. No counterpart in the reference. */
 int uep_debug_link_probe(uep_manager* m, int peer_rank, int64_t bytes, int iters, int use_kernel, float* ms_out);

@@ -13,6 +13,8 @@ namespace uep {
 
 constexpr int kMaxLocalRanks = 8;  // ranks one manager can host on one device (simulated EP)
 constexpr int kMaxPeers = kMaxRanksPerDomain;
+constexpr int kReduceSegments = 16;  // a replica's gradient is released for zeroing in this many pieces
+constexpr unsigned long long kReduceFlagRadix = 64;  // progress word = epoch * radix + segments done
 
 // Device-resident, per hosted rank, immutable after connect. Peer tables are indexed
 // by global rank; entry [my_rank] is this rank's own buffer.
@@ -32,8 +34,10 @@ struct RankDev {
     float* peer_replica_grad[kMaxPeers];
     uint64_t* peer_sync_flags[kMaxPeers];  // each: [N], entry [src] = last epoch src finished sending to that rank
     uint64_t* peer_relay_flags[kMaxPeers]; // each: [R][relay_cap], entry [slot][tile] = epoch in which the master delivered that tile
+    uint64_t* peer_reduce_flags[kMaxPeers]; // each: [N], entry [src] = epoch * 64 + segments of its pulls master rank src has finished
+    int* reduce_counters;    // [kReduceSegments]: CTAs of the running Wgrad reduce that have passed each segment; zero between calls
     DeviceStatus* status;    // mapped pinned host memory
-    // [0] plan epoch, [1] sync epoch: counted on the device (by the CTA that finishes a launch), not
+    // [0] plan epoch, [1] sync epoch, [2] Wgrad-reduce epoch: counted on the device (by the CTA that finishes a launch), not
     // passed by value, so that a captured CUDA graph can be replayed: every replay is a new epoch
     uint64_t* epochs;
 };
@@ -104,6 +108,7 @@ struct ReduceCall {
     int64_t fc1_numel, fc2_numel;
     uint64_t timeout_ns;
     int ctas_per_rank;
+    uint64_t* reduce_epoch;     // the reduce epoch counter of the first hosted rank
     unsigned long long* trace;  // optional: 8 globaltimer stamps per CTA (tuning aid), or null
 };
 cudaError_t launch_grad_reduce(const ReduceCall& call, cudaStream_t stream);

@@ -28,7 +28,7 @@ struct uep_event {
 namespace {
 
 struct ArenaLayout {
-    size_t gather, sync_flags, relay_flags, replica_weight, replica_scale, replica_grad, total;
+    size_t gather, sync_flags, reduce_flags, relay_flags, replica_weight, replica_scale, replica_grad, total;
 };
 
 struct RankHost {
@@ -40,8 +40,8 @@ struct RankHost {
     int32_t* rank_quota_prefix = nullptr;       // [layers][L][D]
     int32_t* physical_loads = nullptr;          // [layers][P]
     int32_t* local_hist = nullptr;              // [Lpad]
-    int* tickets = nullptr;                     // [4]: plan ticket, sync ticket, sync tile counter, spare
-    uint64_t* epochs = nullptr;                 // [2]: plan epoch, sync epoch (device-counted)
+    int* tickets = nullptr;                     // [4 + kReduceSegments]: plan ticket, sync ticket, sync unit counter, spare, reduce segment counters
+    uint64_t* epochs = nullptr;                 // [4]: plan epoch, sync epoch, reduce epoch (device-counted), spare
     int32_t* global_loads = nullptr;            // [L]
     int32_t* loads_per_rank = nullptr;          // [N][L]
     DeviceStatus* status_host = nullptr;        // mapped pinned
@@ -143,6 +143,7 @@ int upload_rank_dev(uep_manager* m, RankHost& r) {
     d.local_hist = r.local_hist;
     d.plan_ticket = r.tickets;
     d.sync_ticket = r.tickets + 1;
+    d.reduce_counters = r.tickets + 4;
     d.epochs = r.epochs;
     d.global_loads = r.global_loads;
     d.loads_per_rank = r.loads_per_rank;
@@ -152,6 +153,7 @@ int upload_rank_dev(uep_manager* m, RankHost& r) {
         if (base == nullptr) return fail(UEP_ERR_STATE, "connect: a peer arena is not mapped");
         d.peer_gather[p] = reinterpret_cast<uint64_t*>(base + m->arena.gather);
         d.peer_sync_flags[p] = reinterpret_cast<uint64_t*>(base + m->arena.sync_flags);
+        d.peer_reduce_flags[p] = reinterpret_cast<uint64_t*>(base + m->arena.reduce_flags);
         d.peer_relay_flags[p] = reinterpret_cast<uint64_t*>(base + m->arena.relay_flags);
         d.peer_replica_weight[p] = base + m->arena.replica_weight;
         d.peer_replica_scale[p] = base + m->arena.replica_scale;
@@ -294,6 +296,7 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
     size_t off = 0;
     m->arena.gather = off;        off = align256(off + sizeof(uint64_t) * 2 * N * m->Lpad);
     m->arena.sync_flags = off;    off = align256(off + sizeof(uint64_t) * N);
+    m->arena.reduce_flags = off;  off = align256(off + sizeof(uint64_t) * N);
     // ready flags of relayed tiles: one word per (replica slot, tile), sized for the smallest tile geometry
     m->relay_cap = 4;
     for (int64_t b : {m->fc1_bytes, m->fc2_bytes, m->fc1_scale_bytes, m->fc2_scale_bytes}) m->relay_cap += static_cast<int>((b + 8191) / 8192);
@@ -327,10 +330,10 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
         UEP_TRY_BAIL(cudaMemset(r.physical_loads, 0, sizeof(int32_t) * static_cast<size_t>(m->P) * cfg->num_layers));
         UEP_TRY_BAIL(cudaMalloc(&r.local_hist, sizeof(int32_t) * m->Lpad));
         UEP_TRY_BAIL(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
-        UEP_TRY_BAIL(cudaMalloc(&r.tickets, sizeof(int) * 4));
-        UEP_TRY_BAIL(cudaMemset(r.tickets, 0, sizeof(int) * 4));
-        UEP_TRY_BAIL(cudaMalloc(&r.epochs, sizeof(uint64_t) * 2));
-        UEP_TRY_BAIL(cudaMemset(r.epochs, 0, sizeof(uint64_t) * 2));
+        UEP_TRY_BAIL(cudaMalloc(&r.tickets, sizeof(int) * (4 + kReduceSegments)));
+        UEP_TRY_BAIL(cudaMemset(r.tickets, 0, sizeof(int) * (4 + kReduceSegments)));
+        UEP_TRY_BAIL(cudaMalloc(&r.epochs, sizeof(uint64_t) * 4));
+        UEP_TRY_BAIL(cudaMemset(r.epochs, 0, sizeof(uint64_t) * 4));
         UEP_TRY_BAIL(cudaMalloc(&r.global_loads, sizeof(int32_t) * m->L));
         UEP_TRY_BAIL(cudaMemset(r.global_loads, 0, sizeof(int32_t) * m->L));
         UEP_TRY_BAIL(cudaMalloc(&r.loads_per_rank, sizeof(int32_t) * static_cast<size_t>(N) * m->L));
@@ -513,8 +516,13 @@ int uep_debug_link_probe(uep_manager* m, int peer_rank, int64_t bytes, int iters
     const int64_t region = static_cast<int64_t>(m->R) * m->weight_stride;
     if (bytes <= 0 || bytes > region || bytes % 16 != 0 || iters <= 0) return fail(UEP_ERR_INVALID, "link_probe: bytes must be a positive multiple of 16 within the replica weight buffer");
     RankHost& r = m->ranks[0];
-    const uint8_t* src = r.arena + m->arena.replica_weight;
-    uint8_t* dst = static_cast<uint8_t*>(r.peer_arena[peer_rank]) + m->arena.replica_weight;
+    // use_kernel bit 1: the other direction (this rank READS the peer's buffer into its own)
+    const bool pull = (use_kernel & 2) != 0;
+    use_kernel &= 1;
+    uint8_t* local = r.arena + m->arena.replica_weight;
+    uint8_t* remote = static_cast<uint8_t*>(r.peer_arena[peer_rank]) + m->arena.replica_weight;
+    const uint8_t* src = pull ? remote : local;
+    uint8_t* dst = pull ? local : remote;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     UEP_CUDA_TRY(cudaEventCreate(&e0));
     UEP_CUDA_TRY(cudaEventCreate(&e1));
@@ -664,6 +672,7 @@ int uep_grad_reduce(uep_manager* m, int layer_id, const int64_t* const* fc1_grad
     // one CTA per SM at most (128 KiB of shared memory each): hosted ranks share the device's SMs
     call.ctas_per_rank = std::max(1, std::min(m->grad_reduce_ctas, m->num_sms / m->nlocal));
     call.trace = m->sync_trace;
+    call.reduce_epoch = m->ranks[0].epochs + 2;
     if (m->R > 0 && m->total_numel > 0) UEP_CUDA_TRY(launch_grad_reduce(call, m->comm_stream));
     return finish_sync_op(m, async_finish, current, done_event);
 }
@@ -817,7 +826,7 @@ int uep_clear_status(uep_manager* m) {
         r.status_host->detail = 0;
         // a timed-out plan may have left the exchange scratch half used: reset it
         UEP_CUDA_TRY(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
-        UEP_CUDA_TRY(cudaMemset(r.tickets, 0, sizeof(int) * 4));
+        UEP_CUDA_TRY(cudaMemset(r.tickets, 0, sizeof(int) * (4 + kReduceSegments)));
     }
     return UEP_OK;
 }
