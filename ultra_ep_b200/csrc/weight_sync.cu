@@ -39,6 +39,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
 #include "internal.h"
 
@@ -77,7 +78,7 @@ struct SyncShared {
     int is_last;
     int n_relay;           // relayed ones among the active masters
     int n_fwd;             // forward entries
-    int fwd_units;         // chunks to forward, all entries
+    int fwd_units;         // forward units: rounds x entries (a unit whose chunk lies behind the expert's end is empty)
     int floor_in;          // adaptive relay: the largest inbound expert count of any rank
     unsigned send_mask[kMaxLocalRanks][3];  // per hosted rank: ranks it writes to (as master or as forwarder)
     unsigned recv_mask[kMaxLocalRanks][3];  // per hosted rank: ranks that write to it
@@ -91,6 +92,7 @@ struct SyncShared {
     short order[kMaxExpertsPerDomain];          // hand-out order of the active masters: relayed ones first
     unsigned char relay_r[kMaxExpertsPerDomain];  // [n_active] 0: direct, else the replica count of a relayed expert
     unsigned char relay_of[kMaxExpertsPerDomain]; // [logical expert of the domain] the same for every expert of the plan
+    unsigned char reps_of[kMaxExpertsPerDomain];  // [logical expert of the domain] its replica count (capped at 255)
     // Addresses are resolved once per CTA: the issuing thread must not chase pointers
     // through global memory for every 32 KiB tile.
     const uint8_t* src[kMaxExpertsPerDomain][4];  // [n_active][shard] master shard base
@@ -107,7 +109,6 @@ struct SyncShared {
     uint8_t* fwd_src_s[kMaxFwd];
     const uint64_t* fwd_flags[kMaxFwd]; // its row of ready flags
     unsigned char fwd_r[kMaxFwd], fwd_k[kMaxFwd], fwd_lr[kMaxFwd];
-    int fwd_unit_start[kMaxFwd + 1];    // prefix of the chunks each entry forwards
     short fwd_dst_start[kMaxFwd + 1];
     uint8_t* fwd_dst_w[kMaxFwdDst];
     uint8_t* fwd_dst_s[kMaxFwdDst];
@@ -115,6 +116,10 @@ struct SyncShared {
     // State of the issuing thread's ring, kept here rather than in its local memory: the kernels that run
     // next to this one evict the L1 lines a stack frame lives in, and every miss would sit on the critical
     // path of a tile.
+    // Ready flags handed to the posting thread: the system-scope fence in front of a flag would make the issuing
+    // thread wait for its own stores in flight; a thread without stores of its own pays almost nothing for it.
+    uint64_t* post[8];
+    volatile int post_head, post_tail, post_done;
     TileRef ring[8];         // the tile held by each stage
     uint64_t* ring_flag[8];  // ready flag to raise once that stage's tile is stored (last tile of a chunk)
     uint64_t* owed[8];       // ready flag owed for the k-th stored tile, slot k % stages
@@ -190,6 +195,9 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         sm.fwd_units = 0;
         sm.floor_in = 1;
         sm.timeout_peer = -1;
+        sm.post_head = 0;
+        sm.post_tail = 0;
+        sm.post_done = 0;
         for (int s = 0; s < 4; ++s) shard_tiles[s] = s < sh.num_shards ? static_cast<int>((sh.bytes[s] + kSyncTile - 1) / kSyncTile) : 0;
         for (int s = 0; s < kSyncStages; ++s) mbar_init(&bars[s], 1);
         fence_mbar_init();
@@ -242,6 +250,12 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
     if (tid == 0) pre_epoch = *call.sync_epoch;
     int pre_owner = -1;
     if (tid < nlocal * R) pre_owner = call.plan[tid / R].p2l[call.my_rank[tid / R] * Lp + M + tid % R];
+    // relay decision: the replica count of logical expert `tid` and the owner of redundant slot `tid` of the group
+    int pre_lc = 1, pre_slot_owner = -1;
+    if (kRelay && relay_on) {
+        if (tid < N * M) pre_lc = call.plan[0].lcnts[tid];
+        if (call.relay_adaptive && tid < N * R) pre_slot_owner = call.plan[0].p2l[(tid / R) * Lp + M + tid % R];
+    }
     if (tid < nlocal * N) {
         sm.peer_weight[tid] = pre_pw;
         sm.peer_scale[tid] = pre_ps;
@@ -254,16 +268,17 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
         const PlanPtrs& plan0 = call.plan[0];
         const int L = min(N * M, kMaxExpertsPerDomain);
         for (int l = tid; l < L; l += blockDim.x) {
-            int reps = relay_on ? plan0.lcnts[l] - 1 : 0;
+            int reps = relay_on ? (l == tid ? pre_lc : plan0.lcnts[l]) - 1 : 0;
             reps = reps < 0 ? 0 : (reps > D - 1 ? D - 1 : reps);
             const bool by_count = reps >= call.relay_min_replicas && reps >= 2 && reps <= kMaxRelayReplicas;
             sm.relay_of[l] = by_count ? static_cast<unsigned char>(reps) : 0;
+            sm.reps_of[l] = static_cast<unsigned char>(reps > 255 ? 255 : reps);
             if (relay_on && call.relay_adaptive && reps > 0) atomicAdd(&sm.rank_out[l / M], reps);
         }
         if (relay_on && call.relay_adaptive) {
             for (int i = tid; i < N * R; i += blockDim.x) {
                 const int r = i / R;
-                if (plan0.p2l[r * Lp + M + i % R] >= 0) atomicAdd(&sm.rank_in[r], 1);
+                if ((i == tid ? pre_slot_owner : plan0.p2l[r * Lp + M + i % R]) >= 0) atomicAdd(&sm.rank_in[r], 1);
             }
         }
         __syncthreads();
@@ -284,8 +299,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                     for (int m = 0; m < M; ++m) {
                         const int l = r * M + m;
                         if (sm.relay_of[l]) continue;
-                        int reps = plan0.lcnts[l] - 1;
-                        reps = reps > D - 1 ? D - 1 : reps;
+                        const int reps = sm.reps_of[l];
                         if (reps > best_reps && reps <= kMaxRelayReplicas) {
                             best = l;
                             best_reps = reps;
@@ -440,22 +454,18 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             sm.fwd_r[f] = static_cast<unsigned char>(my_fwd_r);
             sm.fwd_k[f] = static_cast<unsigned char>(my_fwd_k);
             sm.fwd_lr[f] = static_cast<unsigned char>(lr);
-            // chunks k, k + r, k + 2r, ... of the expert
-            sm.fwd_unit_start[f + 1] = chunks_per_expert > my_fwd_k ? (chunks_per_expert - my_fwd_k + my_fwd_r - 1) / my_fwd_r : 0;
             sm.fwd_dst_start[f + 1] = static_cast<short>(my_fwd_r - 1);
         }
         __syncthreads();
         if (tid == 0) {
             int nf = 0;
             for (int w = 0; w < kSyncThreads / 32; ++w) nf += sm.w_a[w];
-            sm.fwd_unit_start[0] = 0;
             sm.fwd_dst_start[0] = 0;
-            for (int e = 0; e < nf; ++e) {
-                sm.fwd_unit_start[e + 1] += sm.fwd_unit_start[e];
-                sm.fwd_dst_start[e + 1] = static_cast<short>(sm.fwd_dst_start[e + 1] + sm.fwd_dst_start[e]);
-            }
+            for (int e = 0; e < nf; ++e) sm.fwd_dst_start[e + 1] = static_cast<short>(sm.fwd_dst_start[e + 1] + sm.fwd_dst_start[e]);
             sm.n_fwd = nf;
-            sm.fwd_units = sm.fwd_unit_start[nf];
+            // entry f forwards the chunks k_f, k_f + r_f, ...: round j of every entry comes before round j + 1 of any,
+            // which is the order the chunks arrive in; r >= 2, so ceil(chunks / 2) rounds cover every entry
+            sm.fwd_units = nf * ((chunks_per_expert + 1) / 2);
         }
         __syncthreads();
         if (my_fwd_r > 0) {
@@ -484,255 +494,324 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
 
     stamp(1);
     // ---- copy -------------------------------------------------------------------------
-    const int n_relay = kRelay ? sm.n_relay : 0;
-    const int n_direct = sm.n_active - n_relay;
-    const int relay_units = n_relay * chunks_per_expert;
-    const int send_units = relay_units + n_direct * tiles_per_expert;
-    const int total_units = send_units + (kRelay ? sm.fwd_units : 0);
+    // The copy loop exists twice inside the relay-capable kernel: with and without the relay machinery. A rank
+    // that neither scatters nor forwards anything in this launch takes the compact one: the kernel runs once per
+    // layer from a cold instruction cache, and every extra line of code on the path of the first tiles is a miss.
     const uint64_t epoch = sm.epoch;
     DeviceStatus* status0 = call.rank[0]->status;
-    // Work is handed out by an atomic counter: CTAs that run on busy SMs (the reroute and the
-    // model's own kernels run next to this one) simply take less, and replica counts that differ
-    // between masters cannot leave some CTAs with several times the work of others.
     int* unit_counter = call.rank[0]->sync_ticket + 1;
+    auto run_copy = [&](auto relay_tag) {
+        constexpr bool kR = decltype(relay_tag)::value;
+        const int n_relay = kR ? sm.n_relay : 0;
+        const int n_direct = sm.n_active - n_relay;
+        const int relay_units = n_relay * chunks_per_expert;
+        const int send_units = relay_units + n_direct * tiles_per_expert;
+        const int total_units = send_units + (kR ? sm.fwd_units : 0);
+        // Work is handed out by an atomic counter: CTAs that run on busy SMs (the reroute and the
+        // model's own kernels run next to this one) simply take less, and replica counts that differ
+        // between masters cannot leave some CTAs with several times the work of others.
 
-    auto decode_unit = [&](int u) -> Unit {
-        Unit un;
-        if (kRelay && u < relay_units) {
-            const int nr = kRelay ? n_relay : 1;  // (never zero where this branch can run)
-            un.kind = 1;
-            un.who = sm.order[u % nr];
-            un.chunk = u / nr;
-            un.tile = un.chunk * kChunkTiles;
-            un.tile_end = min(un.tile + kChunkTiles, tiles_per_expert);
-        } else if (!kRelay || u < send_units) {
-            const int v = u - relay_units;
-            un.kind = 0;
-            un.who = kRelay ? sm.order[n_relay + v % n_direct] : v % n_direct;
-            un.chunk = 0;
-            un.tile = v / n_direct;
-            un.tile_end = un.tile + 1;
-        } else {
-            const int v = u - send_units;
-            int f = 0;
-            while (f + 1 < sm.n_fwd && v >= sm.fwd_unit_start[f + 1]) ++f;
-            un.kind = 2;
-            un.who = f;
-            un.chunk = sm.fwd_k[f] + (v - sm.fwd_unit_start[f]) * sm.fwd_r[f];
-            un.tile = un.chunk * kChunkTiles;
-            un.tile_end = min(un.tile + kChunkTiles, tiles_per_expert);
-        }
-        return un;
-    };
-    // Source of a tile (a forwarded tile is read from the local slot it landed in).
-    auto tile_source = [&](const TileRef& t) -> const uint8_t* {
-        if (!kRelay || t.kind != 2) return sm.src[t.who][t.shard] + t.offset;
-        return shard_base(sm.fwd_src_w[t.who], sm.fwd_src_s[t.who], sh, t.shard) + t.offset;
-    };
-    // A forwarded chunk may be read once the master has delivered it here: bounded wait on its ready flag.
-    auto wait_chunk = [&](const Unit& un) -> bool {
-        bool ok = true;
-        if (!wait_flag_ge_relaxed(sm.fwd_flags[un.who] + un.chunk, epoch, call.timeout_ns)) {
-            ok = false;
-            report_error(call.rank[sm.fwd_lr[un.who]]->status, UEP_DEV_TIMEOUT_SYNC, un.chunk);
-        }
-        __threadfence_system();        // acquire side of the flag
-        fence_proxy_async_global();    // ... also for the bulk copies that read the chunk next
-        return ok;
-    };
-    // Destinations of a tile: d = first .. first+count-1 -> address (null: skip). A scattered chunk has one
-    // destination, replica (chunk mod r).
-    auto dest_range = [&](const TileRef& t, int& first, int& count) {
-        if (!kRelay || t.kind != 2) {
-            const int r0 = sm.rep_start[t.who], r1 = sm.rep_start[t.who + 1];
-            if (!kRelay || t.kind == 0) {
-                first = r0;
-                count = r1 - r0;
+        auto decode_unit = [&](int u) -> Unit {
+            Unit un;
+            if (kR && u < relay_units) {
+                const int nr = kR ? n_relay : 1;  // (never zero where this branch can run)
+                un.kind = 1;
+                un.who = sm.order[u % nr];
+                un.chunk = u / nr;
+                un.tile = un.chunk * kChunkTiles;
+                un.tile_end = min(un.tile + kChunkTiles, tiles_per_expert);
+            } else if (!kR || u < send_units) {
+                const int v = u - relay_units;
+                un.kind = 0;
+                un.who = kR ? sm.order[n_relay + v % n_direct] : v % n_direct;
+                un.chunk = 0;
+                un.tile = v / n_direct;
+                un.tile_end = un.tile + 1;
             } else {
-                first = r0 + t.chunk % sm.relay_r[t.who];
-                count = first < r1 ? 1 : 0;
+                const int v = u - send_units;
+                const int f = v % sm.n_fwd;
+                un.kind = 2;
+                un.who = f;
+                un.chunk = sm.fwd_k[f] + (v / sm.n_fwd) * sm.fwd_r[f];
+                un.tile = min(un.chunk * kChunkTiles, tiles_per_expert);  // behind the end: an empty unit
+                un.tile_end = min(un.tile + kChunkTiles, tiles_per_expert);
+            }
+            return un;
+        };
+        // Source of a tile (a forwarded tile is read from the local slot it landed in).
+        auto tile_source = [&](const TileRef& t) -> const uint8_t* {
+            if (!kR || t.kind != 2) return sm.src[t.who][t.shard] + t.offset;
+            return shard_base(sm.fwd_src_w[t.who], sm.fwd_src_s[t.who], sh, t.shard) + t.offset;
+        };
+        // A forwarded chunk may be read once the master has delivered it here: bounded wait on its ready flag
+        // (relaxed polls, closed by one acquire load: an acquire does not wait for this thread's own stores in flight).
+        auto chunk_arrived = [&](const Unit& un) -> bool {
+            return un.tile >= un.tile_end || ld_relaxed_sys_u64(sm.fwd_flags[un.who] + un.chunk) >= epoch;
+        };
+        auto wait_chunk = [&](const Unit& un) -> bool {
+            if (un.tile >= un.tile_end) return true;  // empty unit
+            bool ok = true;
+            if (!wait_flag_ge_relaxed(sm.fwd_flags[un.who] + un.chunk, epoch, call.timeout_ns)) {
+                ok = false;
+                report_error(call.rank[sm.fwd_lr[un.who]]->status, UEP_DEV_TIMEOUT_SYNC, un.chunk);
+            }
+            (void)ld_acquire_sys_u64(sm.fwd_flags[un.who] + un.chunk);  // acquire side of the flag
+            fence_proxy_async_global();                                 // ... also for the bulk copies that read the chunk next
+            return ok;
+        };
+        // Destinations of a tile: d = first .. first+count-1 -> address (null: skip). A scattered chunk has one
+        // destination, replica (chunk mod r).
+        auto dest_range = [&](const TileRef& t, int& first, int& count) {
+            if (!kR || t.kind != 2) {
+                const int r0 = sm.rep_start[t.who], r1 = sm.rep_start[t.who + 1];
+                if (!kR || t.kind == 0) {
+                    first = r0;
+                    count = r1 - r0;
+                } else {
+                    first = r0 + t.chunk % sm.relay_r[t.who];
+                    count = first < r1 ? 1 : 0;
+                }
+            } else {
+                first = sm.fwd_dst_start[t.who];
+                count = sm.fwd_dst_start[t.who + 1] - first;
+            }
+        };
+        auto dest_addr = [&](const TileRef& t, int d) -> uint8_t* {
+            uint8_t* w = (!kR || t.kind != 2) ? sm.dst_weight[d] : sm.fwd_dst_w[d];
+            if (w == nullptr) return nullptr;
+            uint8_t* s = (!kR || t.kind != 2) ? sm.dst_scale[d] : sm.fwd_dst_s[d];
+            return shard_base(w, s, sh, t.shard) + t.offset;
+        };
+        // Ready flag of a scattered chunk on the replica that receives it (null: nothing to raise).
+        auto chunk_flag = [&](const Unit& un) -> uint64_t* {
+            const int r0 = sm.rep_start[un.who], r1 = sm.rep_start[un.who + 1];
+            const int d = r0 + un.chunk % sm.relay_r[un.who];
+            if (d >= r1 || sm.dst_flags[d] == nullptr) return nullptr;
+            return sm.dst_flags[d] + un.chunk;
+        };
+
+        if (sm.all_aligned) {
+            if (tid == 0) {
+                TileRef* ring = sm.ring;
+                int* ring_valid = sm.ring_valid;
+                uint64_t** ring_flag = sm.ring_flag;
+                uint64_t** owed = sm.owed;
+                uint32_t phase_bits = 0;           // bit s: parity the next wait on stage s expects
+                bool ok = true;
+                int posted = 0;
+                // hands a ready flag whose chunk is complete to the posting thread (which fences and stores it)
+                auto post_flag = [&](uint64_t* flag) {
+                    while (posted - sm.post_tail >= 8) __nanosleep(50);
+                    sm.post[posted & 7] = flag;
+                    __threadfence_block();
+                    sm.post_head = ++posted;
+                };
+                // The index of the next unit is requested one load ahead, so the round trip of the
+                // atomic overlaps with the copies instead of sitting in front of every load.
+                int pending = atomicAdd(unit_counter, 1);
+                Unit cur{};
+                int cur_tile = 0;
+                bool have_cur = false;
+                bool deferred = false;  // `cur` is a forward chunk that had not arrived when it was taken
+    #pragma unroll
+                for (int s = 0; s < kSyncStages; ++s) owed[s] = nullptr;
+                // Two passes over the same ring: first the send units, then the forward units. A CTA must
+                // not wait for a ready flag while it still holds send tiles it has loaded but not stored:
+                // another CTA (here or on a peer) may be waiting for exactly those. So the first pass stops
+                // at the first forward unit and drains, and only the second pass waits; even there the wait
+                // blocks only once the ring is empty (a chunk that has not arrived is not allowed to hold
+                // up the stores of the chunk in front of it).
+                for (int pass = 0; pass < (kR ? 2 : 1); ++pass) {
+                    const int limit = pass == 0 ? send_units : total_units;
+                    if (pending >= limit && !have_cur) continue;
+                    // Everything about the next tile except the load itself: what it is, where it comes from. Done before
+                    // the wait for the stage to become free, so that this arithmetic hides behind the stores in flight.
+                    const uint8_t* next_src = nullptr;
+                    uint32_t next_bytes16 = 0;
+                    auto prepare_load = [&](int s) {
+                        ring_valid[s] = 0;
+                        if (kR && deferred) return;
+                        while (!have_cur || cur_tile >= cur.tile_end) {
+                            have_cur = false;
+                            if (pending >= limit) return;  // keeps `pending`: a claimed forward unit waits for the second pass
+                            cur = decode_unit(pending);
+                            cur_tile = cur.tile;
+                            have_cur = true;
+                            pending = atomicAdd(unit_counter, 1);
+                            if (kR && cur.kind == 2 && cur_tile < cur.tile_end) {
+                                if (!chunk_arrived(cur)) {
+                                    deferred = true;
+                                    return;
+                                }
+                                (void)wait_chunk(cur);  // arrived: only the acquire side remains
+                            }
+                        }
+                        TileRef t;
+                        t.kind = cur.kind;
+                        t.who = cur.who;
+                        t.chunk = cur.chunk;
+                        t.tile_in_expert = cur_tile;
+                        locate_tile<kSyncTile>(t, sh, shard_tiles);
+                        ++cur_tile;
+                        ring[s] = t;
+                        ring_valid[s] = 1;
+                        ring_flag[s] = (kR && cur.kind == 1 && cur_tile == cur.tile_end) ? chunk_flag(cur) : nullptr;
+                        next_src = tile_source(t);
+                        next_bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
+                    };
+                    // the load itself, once the stage's previous contents have left
+                    auto fire_load = [&](int s) {
+                        if (ring_valid[s] && next_bytes16) {
+                            mbar_expect_tx(&bars[s], next_bytes16);
+                            bulk_load(smem_raw + s * kSyncTile, next_src, next_bytes16, &bars[s]);
+                        }
+                    };
+    #pragma unroll
+                    for (int s = 0; s < kSyncStages; ++s) ring_valid[s] = 0;
+    #pragma unroll
+                    for (int s = 0; s < kSyncStages - 1; ++s) {
+                        prepare_load(s);
+                        fire_load(s);
+                    }
+                    int k = 0;
+                    while (true) {
+                        const int s = k % kSyncStages;
+                        if (!ring_valid[s]) {
+                            if (!(kR && deferred)) break;  // units are handed out in order: nothing is left for this pass
+                            // the ring is empty: now the wait for the chunk may block
+                            bulk_wait_read<0>();
+                            if (!wait_chunk(cur)) ok = false;
+                            deferred = false;
+                            for (int j = 0; j < kSyncStages - 1; ++j) {
+                                prepare_load((k + j) % kSyncStages);
+                                fire_load((k + j) % kSyncStages);
+                            }
+                            if (!ring_valid[s]) break;
+                        }
+                        const TileRef t = ring[s];
+                        const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
+                        if (bytes16) {
+                            if (!mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns)) {
+                                ok = false;
+                                report_error(status0, UEP_DEV_TIMEOUT_COPY, k);
+                                break;  // the stage stays marked valid: its load is waited for below
+                            }
+                            phase_bits ^= 1u << s;
+                        }
+                        ring_valid[s] = 0;
+                        int first, count;
+                        dest_range(t, first, count);
+                        for (int d = first; d < first + count; ++d) {
+                            uint8_t* dst = dest_addr(t, d);
+                            if (dst == nullptr) continue;
+                            if (bytes16) bulk_store(dst, smem_raw + s * kSyncTile, bytes16);
+                            if (static_cast<uint32_t>(t.bytes) != bytes16) {  // up to 15 trailing bytes of a shard
+                                const uint8_t* src = tile_source(t);
+                                for (int b = bytes16; b < t.bytes; ++b) dst[b] = __ldcg(src + b);
+                            }
+                        }
+                        bulk_commit();
+                        // A chunk's ready flag may go out once its stores are complete, not merely read: the flag
+                        // owed for the tile stored kSyncStages-1 iterations ago is due now (groups complete in order,
+                        // so the earlier tiles of that chunk are complete as well).
+                        if (kR) {
+                            uint64_t* due = owed[(k + 1) % kSyncStages];
+                            owed[(k + 1) % kSyncStages] = nullptr;
+                            owed[s] = ring_flag[s];
+                            if (due != nullptr) {
+                                bulk_wait_all<kSyncStages - 1>();
+                                post_flag(due);
+                            }
+                        }
+                        // refill the stage that the previous tile's stores have finished reading
+                        const int refill = (k + kSyncStages - 1) % kSyncStages;
+                        prepare_load(refill);
+                        if (k >= 1) bulk_wait_read<1>();
+                        fire_load(refill);
+                        ++k;
+                    }
+                    if (pass == 0) stamp(2);
+                    bulk_wait_all<0>();
+                    if (kR) {
+    #pragma unroll
+                        for (int s = 0; s < kSyncStages; ++s) {
+                            if (owed[s] != nullptr) post_flag(owed[s]);
+                            owed[s] = nullptr;
+                        }
+                    }
+                    if (!ok) {
+                        // loads still in flight must land before the shared memory is released or reused
+                        for (int s = 0; s < kSyncStages; ++s) {
+                            if (ring_valid[s] && (static_cast<uint32_t>(ring[s].bytes) & ~15u)) {
+                                mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns);
+                            }
+                        }
+                        break;
+                    }
+                }
+                if (kR) {
+                    __threadfence_block();
+                    sm.post_done = 1;
+                }
+                stamp(3);
+            } else if (kR && tid == 32) {
+                // ---- posting thread: raises the ready flags the issuing thread hands over ------------------
+                int tail = 0;
+                while (true) {
+                    const int head = sm.post_head;
+                    if (tail < head) {
+                        __threadfence_block();
+                        uint64_t* flag = sm.post[tail & 7];
+                        __threadfence_system();  // the chunk's stores, seen complete by the issuing thread, before the flag
+                        st_relaxed_sys_u64(flag, epoch);
+                        sm.post_tail = ++tail;
+                    } else if (sm.post_done && tail >= sm.post_head) {
+                        break;
+                    } else {
+                        __nanosleep(100);
+                    }
+                }
             }
         } else {
-            first = sm.fwd_dst_start[t.who];
-            count = sm.fwd_dst_start[t.who + 1] - first;
-        }
-    };
-    auto dest_addr = [&](const TileRef& t, int d) -> uint8_t* {
-        uint8_t* w = (!kRelay || t.kind != 2) ? sm.dst_weight[d] : sm.fwd_dst_w[d];
-        if (w == nullptr) return nullptr;
-        uint8_t* s = (!kRelay || t.kind != 2) ? sm.dst_scale[d] : sm.fwd_dst_s[d];
-        return shard_base(w, s, sh, t.shard) + t.offset;
-    };
-    // Ready flag of a scattered chunk on the replica that receives it (null: nothing to raise).
-    auto chunk_flag = [&](const Unit& un) -> uint64_t* {
-        const int r0 = sm.rep_start[un.who], r1 = sm.rep_start[un.who + 1];
-        const int d = r0 + un.chunk % sm.relay_r[un.who];
-        if (d >= r1 || sm.dst_flags[d] == nullptr) return nullptr;
-        return sm.dst_flags[d] + un.chunk;
-    };
-
-    if (sm.all_aligned) {
-        if (tid == 0) {
-            TileRef* ring = sm.ring;
-            int* ring_valid = sm.ring_valid;
-            uint64_t** ring_flag = sm.ring_flag;
-            uint64_t** owed = sm.owed;
-            uint32_t phase_bits = 0;           // bit s: parity the next wait on stage s expects
-            bool ok = true;
-            // The index of the next unit is requested one load ahead, so the round trip of the
-            // atomic overlaps with the copies instead of sitting in front of every load.
-            int pending = atomicAdd(unit_counter, 1);
-            Unit cur{};
-            int cur_tile = 0;
-            bool have_cur = false;
-#pragma unroll
-            for (int s = 0; s < kSyncStages; ++s) owed[s] = nullptr;
-            // Two passes over the same ring: first the send units, then the forward units. A CTA must
-            // not wait for a ready flag while it still holds send tiles it has loaded but not stored,
-            // or ready flags it has not raised: another CTA (here or on a peer) may be waiting for
-            // exactly those. So the first pass stops at the first forward unit, drains, raises its
-            // flags, and only the second pass waits.
-            for (int pass = 0; pass < (kRelay ? 2 : 1); ++pass) {
-                const int limit = pass == 0 ? send_units : total_units;
-                if (pending >= limit && !have_cur) continue;
-                auto issue_load = [&](int s) {
-                    ring_valid[s] = 0;
-                    if (!have_cur || cur_tile >= cur.tile_end) {
-                        have_cur = false;
-                        if (pending >= limit) return;  // keeps `pending`: a claimed forward unit waits for the second pass
-                        cur = decode_unit(pending);
-                        cur_tile = cur.tile;
-                        have_cur = true;
-                        pending = atomicAdd(unit_counter, 1);
-                        if (kRelay && cur.kind == 2 && !wait_chunk(cur)) ok = false;
-                    }
+            while (true) {
+                __syncthreads();
+                if (tid == 0) sm.s_unit = atomicAdd(unit_counter, 1);
+                __syncthreads();
+                const int u = sm.s_unit;
+                if (u >= total_units) break;
+                const Unit un = decode_unit(u);
+                if (kR && un.kind == 2) {  // forward chunk: one thread waits for the master's delivery
+                    if (tid == 0) (void)wait_chunk(un);
+                    __syncthreads();
+                }
+                for (int tile = un.tile; tile < un.tile_end; ++tile) {
                     TileRef t;
-                    t.kind = cur.kind;
-                    t.who = cur.who;
-                    t.chunk = cur.chunk;
-                    t.tile_in_expert = cur_tile;
+                    t.kind = un.kind;
+                    t.who = un.who;
+                    t.chunk = un.chunk;
+                    t.tile_in_expert = tile;
                     locate_tile<kSyncTile>(t, sh, shard_tiles);
-                    ++cur_tile;
-                    ring[s] = t;
-                    ring_valid[s] = 1;
-                    ring_flag[s] = (kRelay && cur.kind == 1 && cur_tile == cur.tile_end) ? chunk_flag(cur) : nullptr;
-                    const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
-                    if (bytes16) {
-                        mbar_expect_tx(&bars[s], bytes16);
-                        bulk_load(smem_raw + s * kSyncTile, tile_source(t), bytes16, &bars[s]);
-                    }
-                };
-#pragma unroll
-                for (int s = 0; s < kSyncStages; ++s) ring_valid[s] = 0;
-#pragma unroll
-                for (int s = 0; s < kSyncStages - 1; ++s) issue_load(s);
-                int k = 0;
-                while (true) {
-                    const int s = k % kSyncStages;
-                    if (!ring_valid[s]) break;  // units are handed out in order: nothing is left for this pass
-                    const TileRef t = ring[s];
-                    const uint32_t bytes16 = static_cast<uint32_t>(t.bytes) & ~15u;
-                    if (bytes16) {
-                        if (!mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns)) {
-                            ok = false;
-                            report_error(status0, UEP_DEV_TIMEOUT_COPY, k);
-                            break;  // the stage stays marked valid: its load is waited for below
-                        }
-                        phase_bits ^= 1u << s;
-                    }
-                    ring_valid[s] = 0;
+                    const uint8_t* src = tile_source(t);
                     int first, count;
                     dest_range(t, first, count);
                     for (int d = first; d < first + count; ++d) {
                         uint8_t* dst = dest_addr(t, d);
-                        if (dst == nullptr) continue;
-                        if (bytes16) bulk_store(dst, smem_raw + s * kSyncTile, bytes16);
-                        if (static_cast<uint32_t>(t.bytes) != bytes16) {  // up to 15 trailing bytes of a shard
-                            const uint8_t* src = tile_source(t);
-                            for (int b = bytes16; b < t.bytes; ++b) dst[b] = __ldcg(src + b);
-                        }
+                        if (dst != nullptr) copy_plain(src, dst, t.bytes, !kR || t.kind != 2);
                     }
-                    bulk_commit();
-                    // A chunk's ready flag may go out once its stores are complete, not merely read: the flag
-                    // owed for the tile stored kSyncStages-1 iterations ago is due now (groups complete in order,
-                    // so the earlier tiles of that chunk are complete as well).
-                    if (kRelay) {
-                        uint64_t* due = owed[(k + 1) % kSyncStages];
-                        owed[(k + 1) % kSyncStages] = nullptr;
-                        owed[s] = ring_flag[s];
-                        if (due != nullptr) {
-                            bulk_wait_all<kSyncStages - 1>();
-                            __threadfence_system();
-                            st_relaxed_sys_u64(due, epoch);
-                        }
-                    }
-                    // refill the stage that the previous tile's stores have finished reading
-                    const int refill = (k + kSyncStages - 1) % kSyncStages;
-                    if (k >= 1) bulk_wait_read<1>();
-                    issue_load(refill);
-                    ++k;
                 }
-                if (pass == 0) stamp(2);
-                bulk_wait_all<0>();
-                bool any_flag = false;
-                if (kRelay) {
-#pragma unroll
-                    for (int s = 0; s < kSyncStages; ++s) any_flag |= owed[s] != nullptr;
-                }
-                if (any_flag) {
+                if (kR && un.kind == 1) {  // every thread's stores, then the chunk's flag
+                    uint64_t* flag = chunk_flag(un);
                     __threadfence_system();
-#pragma unroll
-                    for (int s = 0; s < kSyncStages; ++s) {
-                        if (owed[s] != nullptr) st_relaxed_sys_u64(owed[s], epoch);
-                        owed[s] = nullptr;
-                    }
-                }
-                if (!ok) {
-                    // loads still in flight must land before the shared memory is released or reused
-                    for (int s = 0; s < kSyncStages; ++s) {
-                        if (ring_valid[s] && (static_cast<uint32_t>(ring[s].bytes) & ~15u)) {
-                            mbar_wait(&bars[s], (phase_bits >> s) & 1u, call.timeout_ns);
-                        }
-                    }
-                    break;
+                    __syncthreads();
+                    if (tid == 0 && flag != nullptr) st_relaxed_sys_u64(flag, epoch);
                 }
             }
-            stamp(3);
         }
+    };
+    if (kRelay && (sm.n_relay != 0 || sm.n_fwd != 0)) {
+        run_copy(std::true_type{});
     } else {
-        while (true) {
-            __syncthreads();
-            if (tid == 0) sm.s_unit = atomicAdd(unit_counter, 1);
-            __syncthreads();
-            const int u = sm.s_unit;
-            if (u >= total_units) break;
-            const Unit un = decode_unit(u);
-            if (kRelay && un.kind == 2) {  // forward chunk: one thread waits for the master's delivery
-                if (tid == 0) (void)wait_chunk(un);
-                __syncthreads();
-            }
-            for (int tile = un.tile; tile < un.tile_end; ++tile) {
-                TileRef t;
-                t.kind = un.kind;
-                t.who = un.who;
-                t.chunk = un.chunk;
-                t.tile_in_expert = tile;
-                locate_tile<kSyncTile>(t, sh, shard_tiles);
-                const uint8_t* src = tile_source(t);
-                int first, count;
-                dest_range(t, first, count);
-                for (int d = first; d < first + count; ++d) {
-                    uint8_t* dst = dest_addr(t, d);
-                    if (dst != nullptr) copy_plain(src, dst, t.bytes, !kRelay || t.kind != 2);
-                }
-            }
-            if (kRelay && un.kind == 1) {  // every thread's stores, then the chunk's flag
-                uint64_t* flag = chunk_flag(un);
-                __threadfence_system();
-                __syncthreads();
-                if (tid == 0 && flag != nullptr) st_relaxed_sys_u64(flag, epoch);
-            }
-        }
+        run_copy(std::false_type{});
     }
     // Order this CTA's copies before its ticket. On the bulk-copy path only thread 0 issued
     // copies and it has already waited for their completion.
@@ -779,6 +858,12 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             }
         }
         stamp(7);
+        unsigned any_recv = 0;
+        for (int lr = 0; lr < nlocal; ++lr) any_recv |= sm.recv_mask[lr][0] | sm.recv_mask[lr][1] | sm.recv_mask[lr][2];
+        if (any_recv == 0) {  // a rank that only sends has nothing to wait for
+            stamp(6);
+            return;
+        }
         for (int i = tid; i < nlocal * N; i += blockDim.x) {
             const int lr = i / N, p = i % N;
             if (sm.recv_mask[lr][p >> 5] & (1u << (p & 31))) {
