@@ -1382,6 +1382,93 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------
+# small fixed cases of single kernels, for profiler captures (a few hundred MB on the device, a handful of launches)
+# ------------------------------------------------------------------------------------------
+def run_profile_case(args):
+    import ctypes as C
+
+    from ultra_ep_b200 import capi, sim
+    from ultra_ep_b200 import workloads as W
+
+    env = Env()
+    torch, dev = env.torch, env.dev
+    lib = capi.lib()
+    case = args.profile_case
+    reps = 3 + 3
+    st = torch.cuda.current_stream().cuda_stream
+
+    def own_plan(cfg):
+        """Plan of rank 0 from this library's solver (device tensors), and rank 0's ids."""
+        N, M, R, L = cfg.ep, cfg.masters, cfg.redundant, cfg.num_experts
+        P, D = N * (M + R), N
+        lpr = torch.from_numpy(W.loads_per_rank(cfg)).to(dev)
+        out = {k: torch.empty(s_, dtype=torch.int32, device=dev) for k, s_ in
+               [("p2l", (P,)), ("l2p", (L, D)), ("lcnts", (L,)), ("quota", (L, D)), ("qp", (L, D)), ("rqp", (L, D))]}
+        gl = torch.empty(L, dtype=torch.int32, device=dev)
+        prm = capi.SolverParams.defaults()
+        capi.check(lib.uep_solve_placement(lpr.data_ptr(), gl.data_ptr(), out["p2l"].data_ptr(), out["l2p"].data_ptr(),
+                                           out["lcnts"].data_ptr(), out["quota"].data_ptr(), out["qp"].data_ptr(),
+                                           out["rqp"].data_ptr(), N, N, M, R, D, C.byref(prm), 0, None, st))
+        return out, torch.from_numpy(W.routing_ids(cfg, 0)).to(dev)
+
+    if case in ("dense", "sparse"):
+        cfg = W.CONFIGS["cfg3_qwen3_235b_fp8"]
+        N, M, R, L, T, K = cfg.ep, cfg.masters, cfg.redundant, cfg.num_experts, cfg.tokens_per_rank, cfg.topk
+        P, D = N * (M + R), N
+        plan, ids = own_plan(cfg)
+        if case == "dense":
+            rmap = torch.zeros((T, L), dtype=torch.bool, device=dev).scatter_(1, ids.long(), True)
+            probs = torch.rand((T, L), dtype=torch.float32, device=dev) * rmap
+            om = torch.empty((T, P), dtype=torch.bool, device=dev)
+            op = torch.empty((T, P), dtype=torch.float32, device=dev)
+            scr = torch.empty(int(lib.uep_reroute_scratch_elems(T, 0, L)), dtype=torch.int32, device=dev)
+            fn = lambda: capi.check(lib.uep_dense_reroute_forward(
+                rmap.data_ptr(), probs.data_ptr(), plan["l2p"].data_ptr(), plan["lcnts"].data_ptr(), plan["rqp"].data_ptr(),
+                om.data_ptr(), op.data_ptr(), scr.data_ptr(), T, L, P, D, 1, 1, st))
+        else:
+            out = torch.empty_like(ids)
+            scr = torch.empty(int(lib.uep_reroute_scratch_elems(T, K, L)), dtype=torch.int32, device=dev)
+            fn = lambda: capi.check(lib.uep_sparse_reroute_i32(
+                ids.data_ptr(), out.data_ptr(), T, K, L, plan["l2p"].data_ptr(), plan["lcnts"].data_ptr(),
+                plan["rqp"].data_ptr(), D, 1, scr.data_ptr(), st))
+    elif case == "gather":
+        rows, H = 16384, 4096
+        src = torch.empty((rows, H), dtype=torch.bfloat16, device=dev).normal_(0, 1e-3)
+        dst = torch.empty_like(src)
+        pos = torch.randperm(rows, device=dev).to(torch.int32)
+        status = torch.zeros(2, dtype=torch.int32, device=dev)
+        fn = lambda: capi.check(lib.uep_gather_rows(src.data_ptr(), pos.data_ptr(), dst.data_ptr(), rows, rows, H * 2,
+                                                    status.data_ptr(), st))
+    elif case in ("reduce", "plan", "sync"):
+        cfg = W.CONFIGS["profile_small_fp8"]
+        args.plan_mode_resolved = 0
+        group, ranks = make_group(env, cfg, 2, case == "reduce", args)
+        ids = [torch.from_numpy(W.routing_ids(cfg, r)).to(dev) for r in ranks]
+        group.update_placement(0, ids)
+        if case == "reduce":
+            M = cfg.masters
+            g1 = [torch.empty((M, cfg.fc1_numel), dtype=torch.float32, device=dev).normal_(0, 1e-4) for _ in ranks]
+            g2 = [torch.empty((M, cfg.fc2_numel), dtype=torch.float32, device=dev).normal_(0, 1e-4) for _ in ranks]
+            t1 = group.pointer_tables([[g[m] for m in range(M)] for g in g1])
+            t2 = group.pointer_tables([[g[m] for m in range(M)] for g in g2])
+            fn = lambda: group.grad_reduce(0, t1, t2)
+        elif case == "sync":
+            masters = Masters(env, cfg, group, ranks)
+            t = masters.tables
+            fn = lambda: group.weight_sync(0, t[0], t[1], t[2], t[3])
+        else:
+            fn = lambda: group.update_placement(1, ids)
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+    times = []
+    for i in range(reps):
+        env.flush_l2()
+        a, b = timed(torch, fn)
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    print(json.dumps({"profile_case": case, "launch_us": [round(x, 1) for x in times]}))
+
+
 def run_ours(args):
     from ultra_ep_b200 import capi
     from ultra_ep_b200 import workloads as W
@@ -1550,9 +1637,13 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip cfg 1, 2, 5 and the EP64 replay")
     ap.add_argument("--no-manager", action="store_true", help="skip the Manager-API section (N > 1)")
     ap.add_argument("--reduce-sms", type=int, default=42, help="CTAs of the Wgrad reduce kernel (reference default 42)")
+    ap.add_argument("--profile-case", default="", choices=["", "dense", "sparse", "gather", "reduce", "plan", "sync"],
+                    help="run six launches of one kernel family on a small fixed case and exit (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.profile_case:
+        run_profile_case(args)
     else:
         run_ours(args)
 

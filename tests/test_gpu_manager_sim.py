@@ -417,6 +417,37 @@ def test_manager_argument_errors(native_lib, cuda_device):
     group.destroy()
 
 
+def test_peer_buffer_addresses_and_scratch_presizing(native_lib, cuda_device):
+    """uep_manager_peer_buffer hands out the address under which a hosted rank reaches a peer's replica buffers
+    (on one device: the peer's own buffer); the link probe refuses a simulated group; with reroute_max_tokens the
+    reroute scratch has its size from the start."""
+    lib = capi.lib()
+    mcfg = sim.make_config(4, 2, 2, 1, fc1_numel=1024, fc2_numel=512, weight_elem_bytes=2, fc1_scale_numel=16,
+                           fc2_scale_numel=8, sim=True, is_train=True)
+    mcfg.reroute_max_tokens = 4096
+    mcfg.reroute_max_topk = 4
+    group = sim.SimGroup(mcfg)
+    for buf in (capi.BUF_REPLICA_WEIGHT, capi.BUF_REPLICA_SCALE, capi.BUF_REPLICA_GRAD):
+        for local in range(4):
+            for peer in range(4):
+                out = C.c_void_p()
+                capi.check(lib.uep_manager_peer_buffer(group.handle, local, peer, buf, C.byref(out)))
+                assert out.value == group.buffer(peer, buf).data_ptr()
+    out = C.c_void_p()
+    assert lib.uep_manager_peer_buffer(group.handle, 0, 9, capi.BUF_REPLICA_WEIGHT, C.byref(out)) == -1
+    assert lib.uep_manager_peer_buffer(group.handle, 0, 1, capi.BUF_P2L, C.byref(out)) == -1
+    ms = C.c_float()
+    assert lib.uep_debug_link_probe(group.handle, 1, 1024, 1, 0, C.byref(ms)) == -3  # needs real peers
+    # reroutes up to the stated bound work right away (and larger ones still grow the buffer)
+    ids = [torch.randint(0, 8, (4096, 4), dtype=torch.int32, device=cuda_device) for _ in range(4)]
+    group.update_placement(0, ids)
+    phys = group.reroute_sparse(0, ids)
+    torch.cuda.synchronize()
+    group.check_status()
+    assert all(int(p.min()) >= 0 and int(p.max()) < 16 for p in phys)
+    group.destroy()
+
+
 def test_legacy_placement_mode(native_lib, cuda_device):
     """legacy_placement=True through the manager: the counts-only greedy plan from the gathered loads, round-robin
     reroute (dense and sparse) over an expert's instances, weights synced to every instance."""

@@ -205,3 +205,64 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert d["higher_is_better"] is False and d["value"] > 0 and d["gpu_launches"] == 0
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"] == {"value": d["value"], "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+TEARDOWN_WORKER = r'''
+import os, sys, time
+sys.path.insert(0, os.environ["UEP_ROOT"])
+import torch.distributed as dist
+dist.init_process_group("gloo")
+from ultra_ep_b200.manager import Manager
+
+rank = dist.get_rank()
+out = os.environ["UEP_OUT"]
+
+
+class FakeRuntime:  # stands in for the native manager: records WHEN the arena would be freed
+    def destroy(self):
+        open(os.path.join(out, f"freed{rank}"), "w").write(repr(time.time()))
+
+
+class FakeProfiler:
+    def close(self):
+        pass
+
+
+mgr = Manager.__new__(Manager)  # the constructor needs a GPU; teardown ordering does not
+mgr.runtime, mgr.group, mgr.explicitly_destroy, mgr._load_profiler = FakeRuntime(), dist.group.WORLD, False, FakeProfiler()
+dist.barrier()
+if rank == 1:
+    time.sleep(1.5)  # rank 1 is still "computing": its kernels may still store into rank 0's arena
+open(os.path.join(out, f"entered{rank}"), "w").write(repr(time.time()))
+del mgr  # explicitly_destroy=False: releasing the last reference runs the ordered teardown
+assert os.path.exists(os.path.join(out, f"freed{rank}"))
+
+# without a usable group nothing is freed: the native layer is told to keep the memory
+class Abandoned(FakeRuntime):
+    abandoned = False
+    def abandon(self):
+        Abandoned.abandoned = True
+    def destroy(self):
+        raise SystemExit("freed peer-visible memory without a barrier")
+m2 = Manager.__new__(Manager)
+m2.runtime, m2.group, m2.explicitly_destroy, m2._load_profiler = Abandoned(), "not a process group", False, FakeProfiler()
+assert m2._teardown() is False and Abandoned.abandoned and m2.runtime is None
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def test_teardown_waits_for_every_rank_over_gloo(tmp_path):
+    """A rank's peer-visible arena is freed only after EVERY rank of the group has entered teardown (the peers'
+    kernels store into it), also on the implicit path (explicitly_destroy=False, last reference dropped); and
+    when no barrier can be made, nothing is freed."""
+    script = tmp_path / "teardown_worker.py"
+    script.write_text(TEARDOWN_WORKER)
+    env = dict(os.environ, UEP_ROOT=ROOT, UEP_OUT=str(tmp_path), CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+         "--master-port", "29633", str(script)], env=env, capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    t = {name: float((tmp_path / name).read_text()) for name in ("entered0", "entered1", "freed0", "freed1")}
+    assert t["freed0"] >= t["entered1"] and t["freed1"] >= t["entered0"]
+    assert t["freed0"] - t["entered0"] > 1.0  # rank 0 really waited for the late rank

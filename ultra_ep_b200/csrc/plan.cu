@@ -8,11 +8,13 @@
 //   * every CTA of a rank counts a slice of the routing input into shared memory and
 //     adds its partial to the rank's row in global memory;
 //   * the CTA that takes the last ticket owns the rest: it stores the row into every
-//     peer's gather buffer with plain peer stores followed by a system-scope release of
-//     an epoch flag, waits (bounded) for the peers' flags, reduces the matrix and runs
-//     the solver (solver.cuh). No CTA ever waits on another CTA of its own rank.
+//     peer's gather buffer as self-validating 64-bit words (epoch tag << 32 | count; an
+//     aligned 8-byte store is single-copy atomic, so a word needs neither a fence nor a
+//     flag), polls its own buffer (bounded) until every rank's words carry this epoch's
+//     tag, reduces the matrix and runs the solver (solver.cuh). No CTA ever waits on
+//     another CTA of its own rank.
 // The gather buffers are double-buffered by epoch parity: a peer can be at most one
-// call ahead, because it cannot pass call e+1 without this rank's flag for e+1.
+// call ahead, because it cannot pass call e+1 without this rank's row for e+1.
 //
 // With several ranks hosted on one device (simulated EP) the same kernel runs all of
 // them in one cooperative launch, so the ranks that wait for each other are co-resident.
@@ -277,8 +279,10 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 if (r0 + u < N) {
+                    // one time limit for the whole gather: once a wait has run out, no other word is waited for
                     if (static_cast<uint32_t>(w[u] >> 32) != tag &&
-                        !wait_tagged_word(gathered + static_cast<int64_t>(r0 + u) * Lpad + i, tag, call.timeout_ns, w[u])) {
+                        !wait_tagged_word(gathered + static_cast<int64_t>(r0 + u) * Lpad + i, tag,
+                                          *reinterpret_cast<volatile int*>(&s_timeout_peer) >= 0 ? 0 : call.timeout_ns, w[u])) {
                         atomicMax(&s_timeout_peer, r0 + u);
                         w[u] = 0;
                     }

@@ -582,6 +582,8 @@ __global__ void __launch_bounds__(kRerouteThreads) sparse_count_kernel(Batch<Spa
     const IdT* keys = static_cast<const IdT*>(a.ids);
     const int64_t n = static_cast<int64_t>(a.T) * K;
     const int64_t begin = static_cast<int64_t>(blockIdx.x) * kSparseTileEntries;
+    // (a tile behind this rank's entries: the second pass launches the same grid and returns at the same test, so
+    // every count it reads has been written by this pass, whatever the scratch buffer held before)
     if (begin >= n) return;
     int32_t* hist = reinterpret_cast<int32_t*>(smem_raw);
     for (int i = threadIdx.x; i < L; i += blockDim.x) hist[i] = 0;
@@ -1015,7 +1017,8 @@ int uep_sparse_reroute_i64(const int64_t* ids, int64_t* out, int T, int K, int L
 //
 // Limits and rules:
 //   * the per-tile counts must fit the array: ceil(T*K / 2048) * L + 4 <= 262144 int32 (1 MiB);
-//     e.g. 131072 entries (16384 tokens x top-8) with up to 4096 experts, or 1M entries with 512.
+//     e.g. 131072 entries (16384 tokens x top-8) with up to 4095 experts, or 511 tiles (1,046,528
+//     entries) with 512 experts: the four spare words count against the limit.
 //     Larger problems are refused with UEP_ERR_INVALID and a message, nothing is launched;
 //   * the array is shared by every call on a device and keeps the previous call's counts. The
 //     count pass overwrites every element the second pass reads, so nothing has to start at

@@ -133,6 +133,10 @@ public:
         cfg.weight_sync_num_sms = sms ? std::atoi(sms) : 0;
         const char* to = std::getenv("ULTRA_EP_WAIT_TIMEOUT_MS");
         cfg.wait_timeout_ms = to ? std::atoi(to) : 0;
+        const char* mt = std::getenv("ULTRA_EP_REROUTE_MAX_TOKENS");  // > 0: the reroute scratch never grows after construction
+        cfg.reroute_max_tokens = mt ? std::atoi(mt) : 0;
+        const char* mk = std::getenv("ULTRA_EP_REROUTE_MAX_TOPK");
+        cfg.reroute_max_topk = mk ? std::atoi(mk) : 0;
         check(uep_manager_create(&cfg, &m_), "Manager");
         M_ = num_local_master_experts;
         R_ = num_local_redundant_experts;
@@ -169,14 +173,25 @@ public:
 
     ~Manager() {
         if (!available_) return;
-        if (!explicitly_destroy_) {
+        // The arena is mapped by the peers, and their kernels store into it. It may only be freed behind a barrier
+        // over the group, which this destructor cannot make (the reference's destructor can: its barrier is
+        // NVSHMEM's, csrc/ultra_ep.cpp:534-549). The Python Manager makes it and then calls destroy(); if nobody
+        // did, a group of several ranks keeps the memory until the process exits instead of freeing it under a peer.
+        if (!explicitly_destroy_ && g_rt.num_ranks <= 1) {
             uep_manager_destroy(m_);  // no exception from a destructor
-            m_ = nullptr;
-            available_ = false;
         } else {
-            std::printf("WARNING: destroy() was not called before UltraEP manager destruction, which can leak resources.\n");
+            std::printf("WARNING: destroy() was not called before UltraEP manager destruction; its peer-visible memory "
+                        "stays allocated until the process exits.\n");
             std::fflush(stdout);
         }
+        m_ = nullptr;
+        available_ = false;
+    }
+
+    // Gives up the native resources without freeing them (no barrier over the group could be made).
+    void abandon() {
+        m_ = nullptr;
+        available_ = false;
     }
 
     void destroy() {
@@ -486,6 +501,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              py::arg("weight_sync_plan_mode") = 1, py::arg("weight_sync_relay_min_replicas") = 4,
              py::arg("weight_sync_relay_max_relays") = 8, py::arg("weight_sync_relay_min_fanout_gain") = 2)
         .def("destroy", &Manager::destroy)
+        .def("abandon", &Manager::abandon)
         .def("is_available", &Manager::is_available)
         .def("update_placement", &Manager::update_placement)
         .def("update_placement_sparse", &Manager::update_placement_sparse)

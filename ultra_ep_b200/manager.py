@@ -98,14 +98,10 @@ class Manager:
         self.quota_kernel_stage = tuning.quota_kernel_stage
         self.quota_reroute_interleave = tuning.quota_reroute_interleave
         plan_mode, plan_mode_id = tuning.weight_sync_plan_mode, tuning.weight_sync_plan_mode_id
-        # As in the reference, the default (adaptive) falls back to the direct fan-out when the NVLink
-        # domain has at most 8 ranks. An explicit force_relay is honoured at any size: here relaying is
-        # scatter + replica-to-replica forward inside the one copy kernel, not a second stage.
-        if self.nvl_domain_size <= 8 and plan_mode == "adaptive":
-            if self.rank == 0:
-                print(f"UltraEP: NVL domain size <= 8; forcing weight_sync plan mode to direct (was {plan_mode}).",
-                      flush=True)
-            plan_mode, plan_mode_id = "direct", 0
+        # The reference forces the direct fan-out when the NVLink domain has at most 8 ranks, because its relay is a
+        # second stage with its own launches. Here relaying is scatter + replica-to-replica forward inside the one
+        # copy kernel and the adaptive mode only relays what relieves the busiest sender of the layer's plan, so the
+        # default (adaptive) stays adaptive at any domain size.
         self.weight_sync_plan_mode = plan_mode
         self.weight_sync_relay_min_replicas = tuning.weight_sync_relay_min_replicas
         self.weight_sync_relay_max_relays = tuning.weight_sync_relay_max_relays
@@ -214,12 +210,41 @@ class Manager:
 
     def destroy(self):
         assert self.explicitly_destroy
-        if self.runtime is not None:
-            torch.cuda.synchronize()
+        self._teardown()
+
+    def _teardown(self) -> bool:
+        """Collective release of the native resources: every rank first finishes its own work and then
+        waits for all the others, because the peers hold mappings of this rank's arena and their kernels store
+        into it; only then is it freed. Returns False (and frees nothing) when the barrier cannot be made, e.g.
+        because the process group is gone: the native layer then keeps the arena until the process exits rather
+        than free memory a peer may still write."""
+        if self.runtime is None:
+            return True
+        try:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
             dist.barrier(group=self.group)  # no peer may still be writing into this rank's slots
-            self._load_profiler.close()
-            self.runtime.destroy()
+        except Exception as e:  # group destroyed, interpreter shutting down, ...
+            print(f"UltraEP: manager teardown without a group barrier ({type(e).__name__}); the peer-visible "
+                  "memory is kept until the process exits", flush=True)
+            abandon = getattr(self.runtime, "abandon", None)
+            if abandon is not None:
+                abandon()
+            self.runtime = None
+            return False
+        self._load_profiler.close()
+        self.runtime.destroy()
         self.runtime = None
+        return True
+
+    def __del__(self):
+        # explicitly_destroy=False: the same ordered release when the last reference goes (every rank drops its
+        # manager at the same point of the program, as with the reference's destructor-side barrier)
+        try:
+            if getattr(self, "runtime", None) is not None and not self.explicitly_destroy:
+                self._teardown()
+        except Exception:
+            pass
 
     # -- virtual layers --------------------------------------------------------------------
     def allocate_microbatch_slot(self, real_layer_id: int) -> int:
