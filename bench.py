@@ -372,7 +372,7 @@ def link_volumes(cfg, plan, ranks, relay_of=None):
 
 def relay_selection(cfg, plan, plan_mode, relay_min):
     """Which experts weight_sync relays: the rule of the kernel (ultra_ep_b200/csrc/weight_sync.cu), restated."""
-    if plan_mode == 0:
+    if plan_mode == 0 or cfg.ep <= 2:  # two ranks: the library launches the direct kernel whatever the mode
         return None
     M, R, N = cfg.masters, cfg.redundant, cfg.ep
     Lp = M + R
@@ -990,14 +990,15 @@ def run_backward(env, args, peak_hbm, link):
         ach = hbm_bytes / 1e9 / (red_ms / 1e3)
         out["grad_reduce_roofline"] = {"kernel": "grad_reduce_kernel", "bound": "hbm", "achieved": round(ach, 1), "peak": peak_hbm,
                                        "unit": "GB/s", "frac": round(ach / peak_hbm, 4), "algorithmic_bytes_per_launch": hbm_bytes,
-                                       "ctas": args.reduce_sms,
-                                       "note": "simulated EP: masters read+written, replicas read+zeroed, all through HBM"}
+                                       "ctas": 8 * min(args.reduce_sms, lib.uep_manager_num_sms(group.handle) // 8),
+                                       "note": "simulated EP: masters read+written, replicas read+zeroed, all through HBM; "
+                                               "ctas = all eight hosted ranks' CTAs of the one launch"}
     else:
         busiest = max(env.max_each([float(link_bytes)]))
         ach = busiest / 1e9 / (red_ms / 1e3)
         rl = {"kernel": "grad_reduce_kernel", "bound": "nvlink", "achieved": round(ach, 1), "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s",
               "frac": round(ach / NVLINK_NOMINAL_GBS, 4), "algorithmic_bytes_per_launch": int(busiest), "ctas": args.reduce_sms,
-              "note": "bytes = replica gradients the busiest GPU pulls in (it pushes as many zeros)"}
+              "note": "bytes = replica gradients the busiest GPU pulls in over NVLink (used replica slots are cleared by the rank that hosts them, locally)"}
         if link:
             best = max(link.get("copy_engine_gbs") or 0.0, link.get("kernel_gbs") or 0.0)
             if best > 0:

@@ -931,7 +931,9 @@ int weight_sync_tile_bytes() { return sync_geometry().tile_kib * 1024; }
 cudaError_t launch_weight_sync(const SyncCall& call, cudaStream_t stream) {
     const SyncGeometry& g = sync_geometry();
     const size_t smem = sync_smem_bytes(g);
-    const bool relay = call.relay_min_replicas > 0;
+    // two ranks: an expert has at most one replica away from its master, nothing can be relayed; the
+    // compact kernel is the same on every rank because N is
+    const bool relay = call.relay_min_replicas > 0 && call.N > 2;
     const void* fn = relay ? g.fn_relay : g.fn;
     static const void* attr_set_for[2] = {nullptr, nullptr};
     if (attr_set_for[relay] != fn) {
