@@ -22,7 +22,6 @@
 #include <cooperative_groups.h>
 
 #include <atomic>
-#include <cstdlib>
 
 #include <algorithm>
 #include <cstring>
@@ -355,15 +354,6 @@ cudaError_t launch_plan(const PlanCall& call, cudaStream_t stream) {
     const size_t smem = plan_smem_bytes(call.N, call.G, call.M);
     cudaError_t e = ensure_smem(reinterpret_cast<const void*>(plan_kernel), smem);
     if (e != cudaSuccess) return e;
-    // Tuning aid: UEP_PLAN_CARVEOUT=1 asks for the largest shared-memory carve-out, so that the SMs need no
-    // reconfiguration between this kernel and the weight_sync kernel that follows it.
-    static const bool carve = [] {
-        const char* v = std::getenv("UEP_PLAN_CARVEOUT");
-        return v != nullptr && v[0] == '1' &&
-               cudaFuncSetAttribute(reinterpret_cast<const void*>(plan_kernel), cudaFuncAttributePreferredSharedMemoryCarveout,
-                                    cudaSharedmemCarveoutMaxShared) == cudaSuccess;
-    }();
-    (void)carve;
     const dim3 grid(call.nlocal * call.ctas_per_rank), block(kPlanThreads);
     count_launch();
     if (call.nlocal > 1) {
