@@ -162,14 +162,24 @@ class Env:
             self.dist = dist
         self.flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=self.dev)
         self.flush_read = torch.zeros(FLUSH_BYTES // 4, dtype=torch.int32, device=self.dev)
+        self._align_word = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.failures = []  # parity failures (messages)
 
     def flush_l2(self):
         """Write a buffer twice the size of L2, then read another one: the step starts with a cold
         L2 that holds no dirty lines of the flush (their write-back would otherwise land inside the
         timed step and be charged to it)."""
+        self.align()
         self.flush.zero_()
         self.flush_read.sum()
+
+    def align(self):
+        """Line the ranks up ON THE DEVICE (a one-word all-reduce queued on the stream; the host does not wait):
+        the ranks enter every timed step together, as they enter a layer behind the dispatch of the layer
+        before. Without it a rank that had little to copy in one step starts the next step early, waits in the
+        load exchange for the others, and that wait is charged to the next step's slowest-rank time."""
+        if self.world > 1:
+            self.dist.all_reduce(self._align_word)
 
     def barrier(self):
         self.torch.cuda.synchronize()
@@ -1588,6 +1598,9 @@ def run_ours(args):
                 "redundant_per_rank": cfg.redundant, "expert_bytes": cfg.expert_bytes, "zipf_s": cfg.zipf_s,
                 "weight_sync_plan_mode": args.plan_mode_resolved,
                 "l2": "between timed steps a 256 MiB buffer is written, then a second 256 MiB buffer is read",
+                "rank_alignment": ("none (one process)" if world == 1 else
+                                   "a one-word NCCL all-reduce is queued on the stream in front of every L2 flush, outside the timed "
+                                   "events: the ranks enter each step together; the host never waits inside the loop"),
                 "microbatch_pool": pool,
             },
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "parity": parity, "roofline": roofline,

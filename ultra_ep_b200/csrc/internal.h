@@ -18,12 +18,13 @@ constexpr unsigned long long kReduceFlagRadix = 64;  // progress word = epoch * 
 
 // Device-resident, per hosted rank, immutable after connect. Peer tables are indexed
 // by global rank; entry [my_rank] is this rank's own buffer.
+constexpr int kPlanMaxCtas = 32;  // CTAs of one rank in the plan kernel
+
 struct RankDev {
     int my_rank;
     int num_ranks;
     // plan exchange
-    int32_t* local_hist;     // [Lpad], zero between calls
-    int* plan_ticket;        // zero between calls
+    uint64_t* hist_parts;    // [kPlanMaxCtas][Lpad] words, (epoch tag << 32) | partial count of one CTA of the plan kernel
     uint64_t* peer_gather[kMaxPeers];  // each: [2][N][Lpad] words, (epoch tag << 32) | token count
     int32_t* global_loads;   // [L]
     int32_t* loads_per_rank; // [N][L] latest gathered matrix (contiguous copy)

@@ -39,8 +39,8 @@ struct RankHost {
     int32_t* plan_blob = nullptr;               // [layers][stride]
     int32_t* rank_quota_prefix = nullptr;       // [layers][L][D]
     int32_t* physical_loads = nullptr;          // [layers][P]
-    int32_t* local_hist = nullptr;              // [Lpad]
-    int* tickets = nullptr;                     // [4 + kReduceSegments]: plan ticket, sync ticket, sync unit counter, spare, reduce segment counters
+    uint64_t* hist_parts = nullptr;             // [kPlanMaxCtas][Lpad]
+    int* tickets = nullptr;                     // [4 + kReduceSegments]: spare, sync ticket, sync unit counter, spare, reduce segment counters
     uint64_t* epochs = nullptr;                 // [4]: plan epoch, sync epoch, reduce epoch (device-counted), spare
     int32_t* global_loads = nullptr;            // [L]
     int32_t* loads_per_rank = nullptr;          // [N][L]
@@ -140,8 +140,7 @@ int upload_rank_dev(uep_manager* m, RankHost& r) {
     std::memset(&d, 0, sizeof(d));
     d.my_rank = r.rank;
     d.num_ranks = m->N;
-    d.local_hist = r.local_hist;
-    d.plan_ticket = r.tickets;
+    d.hist_parts = r.hist_parts;
     d.sync_ticket = r.tickets + 1;
     d.reduce_counters = r.tickets + 4;
     d.epochs = r.epochs;
@@ -174,7 +173,7 @@ void free_rank(RankHost& r, int my_rank_count) {
     cudaFree(r.plan_blob);
     cudaFree(r.rank_quota_prefix);
     cudaFree(r.physical_loads);
-    cudaFree(r.local_hist);
+    cudaFree(r.hist_parts);
     cudaFree(r.tickets);
     cudaFree(r.epochs);
     cudaFree(r.global_loads);
@@ -328,8 +327,8 @@ int uep_manager_create(const uep_config* cfg, uep_manager** out) {
         UEP_TRY_BAIL(cudaMalloc(&r.rank_quota_prefix, sizeof(int32_t) * static_cast<size_t>(m->L) * m->D * cfg->num_layers));
         UEP_TRY_BAIL(cudaMalloc(&r.physical_loads, sizeof(int32_t) * static_cast<size_t>(m->P) * cfg->num_layers));
         UEP_TRY_BAIL(cudaMemset(r.physical_loads, 0, sizeof(int32_t) * static_cast<size_t>(m->P) * cfg->num_layers));
-        UEP_TRY_BAIL(cudaMalloc(&r.local_hist, sizeof(int32_t) * m->Lpad));
-        UEP_TRY_BAIL(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
+        UEP_TRY_BAIL(cudaMalloc(&r.hist_parts, sizeof(uint64_t) * kPlanMaxCtas * m->Lpad));
+        UEP_TRY_BAIL(cudaMemset(r.hist_parts, 0, sizeof(uint64_t) * kPlanMaxCtas * m->Lpad));
         UEP_TRY_BAIL(cudaMalloc(&r.tickets, sizeof(int) * (4 + kReduceSegments)));
         UEP_TRY_BAIL(cudaMemset(r.tickets, 0, sizeof(int) * (4 + kReduceSegments)));
         UEP_TRY_BAIL(cudaMalloc(&r.epochs, sizeof(uint64_t) * 4));
@@ -825,7 +824,7 @@ int uep_clear_status(uep_manager* m) {
         r.status_host->code = 0;
         r.status_host->detail = 0;
         // a timed-out plan may have left the exchange scratch half used: reset it
-        UEP_CUDA_TRY(cudaMemset(r.local_hist, 0, sizeof(int32_t) * m->Lpad));
+        UEP_CUDA_TRY(cudaMemset(r.hist_parts, 0, sizeof(uint64_t) * kPlanMaxCtas * m->Lpad));
         UEP_CUDA_TRY(cudaMemset(r.tickets, 0, sizeof(int) * (4 + kReduceSegments)));
     }
     return UEP_OK;

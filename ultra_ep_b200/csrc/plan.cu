@@ -5,14 +5,14 @@
 // device copy, NVSHMEM fcollect, reduce kernel, six memsets, solver kernel;
 // csrc/ultra_ep.cpp:676-745 and csrc/kernels/placement.cu:1602-1663 of the reference)
 // is one kernel here:
-//   * every CTA of a rank counts a slice of the routing input into shared memory and
-//     adds its partial to the rank's row in global memory;
-//   * the CTA that takes the last ticket owns the rest: it stores the row into every
-//     peer's gather buffer as self-validating 64-bit words (epoch tag << 32 | count; an
-//     aligned 8-byte store is single-copy atomic, so a word needs neither a fence nor a
-//     flag), polls its own buffer (bounded) until every rank's words carry this epoch's
-//     tag, reduces the matrix and runs the solver (solver.cuh). No CTA ever waits on
-//     another CTA of its own rank.
+//   * every CTA of a rank counts a slice of the routing input into shared memory; all but the
+//     rank's first CTA store their partial counts as self-validating 64-bit words (epoch
+//     tag << 32 | count; an aligned 8-byte store is single-copy atomic, so a word needs neither
+//     a fence nor a flag) into a row of their own and are done;
+//   * the rank's first CTA owns the rest: it adds up the partials (bounded wait on words of
+//     its own launch's CTAs, none of which waits for it), stores the row into every peer's
+//     gather buffer as the same kind of words, polls its own buffer (bounded) until every
+//     rank's words carry this epoch's tag, reduces the matrix and runs the solver (solver.cuh).
 // The gather buffers are double-buffered by epoch parity: a peer can be at most one
 // call ahead, because it cannot pass call e+1 without this rank's row for e+1.
 //
@@ -198,7 +198,6 @@ __global__ void __launch_bounds__(256) init_master_kernel(int32_t* p2l, int32_t*
 // The fused per-layer plan kernel. gridDim.x = nlocal * ctas_per_rank.
 __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     extern __shared__ __align__(128) char smem_raw[];
-    __shared__ int s_is_last;
     __shared__ int s_timeout_peer;
     __shared__ uint64_t s_epoch;
 
@@ -211,50 +210,71 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(PlanCall call) {
     const int tid = threadIdx.x;
     const unsigned long long t_start = call.trace != nullptr ? global_timer_ns() : 0ull;
 
-    // 1. histogram slice -> shared -> this rank's row in global memory
+    // 1. histogram slice -> shared. The rank's first CTA owns the rest of the kernel; the others hand it their
+    //    partial counts as self-validating words (epoch tag << 32 | count) in a row of their own and are done:
+    //    no atomics on a common row, no fence, no ticket, and the owner sees a partial one memory round trip
+    //    after it was stored. The owner waits (bounded) for CTAs of its own launch; none of them waits for it,
+    //    so they need not be resident at the same time.
     int32_t* hist = reinterpret_cast<int32_t*>(smem_raw);
     for (int i = tid; i < L; i += blockDim.x) hist[i] = 0;
+    if (tid == 0) {
+        s_timeout_peer = -1;
+        // the epoch this launch opens: the owner stores it once it holds every partial, so every CTA of the
+        // launch reads the same value here
+        s_epoch = *reinterpret_cast<volatile uint64_t*>(rk.epochs) + 1;
+    }
     __syncthreads();
     histogram_slice(call.input_kind, call.input[local], call.T[local], call.K_or_L, L, part, call.ctas_per_rank, hist);
     __syncthreads();
-    for (int i = tid; i < L; i += blockDim.x) {
-        if (hist[i]) atomicAdd(rk.local_hist + i, hist[i]);
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const int ticket = atomicAdd(rk.plan_ticket, 1);
-        s_is_last = (ticket == call.ctas_per_rank - 1) ? 1 : 0;
-        s_timeout_peer = -1;
-        if (s_is_last) {  // one CTA per rank and launch gets here: it opens the next epoch
-            s_epoch = rk.epochs[0] + 1;
-            rk.epochs[0] = s_epoch;
-        }
-    }
-    __syncthreads();
-    if (!s_is_last) return;
-    __threadfence();
-    auto stamp = [&](int slot) {
-        if (call.trace != nullptr && tid == 0) call.trace[local * 8 + slot] = global_timer_ns();
-    };
-    stamp(0);
-    if (call.trace != nullptr && tid == 0) call.trace[local * 8 + 5] = t_start;  // when this CTA started
-
-    // 2. the last CTA publishes the row to every rank (itself included) and resets the scratch.
-    //    Every 64-bit word carries the epoch beside its count, so a row needs neither a fence nor
-    //    a flag: one NVLink crossing, and the reader knows a word is this layer's when it sees it.
     const uint64_t epoch = s_epoch;
-    const int slot = static_cast<int>(epoch & 1ull);
     // never zero (the buffers start zeroed), period 2^32 - 1: an odd period, so the word that carried the same
     // tag one period ago sat in the other parity slot and cannot be mistaken for this epoch's
     const uint32_t tag = static_cast<uint32_t>(epoch % 0xFFFFFFFFull) + 1u;
-    const int me = rk.my_rank;
-    for (int i = tid; i < L; i += blockDim.x) {
-        hist[i] = __ldcg(rk.local_hist + i);
-        rk.local_hist[i] = 0;
+    if (part != 0) {
+        uint64_t* row = rk.hist_parts + static_cast<int64_t>(part) * Lpad;
+        for (int i = tid; i < L; i += blockDim.x) st_relaxed_sys_u64(row + i, tag_word(tag, static_cast<uint32_t>(hist[i])));
+        return;
     }
-    if (tid == 0) *rk.plan_ticket = 0;
+    auto stamp = [&](int slot) {
+        if (call.trace != nullptr && tid == 0) call.trace[local * 8 + slot] = global_timer_ns();
+    };
+    if (call.trace != nullptr && tid == 0) call.trace[local * 8 + 5] = t_start;  // when this CTA started
+    for (int i = tid; i < L; i += blockDim.x) {
+        int32_t total = hist[i];
+        for (int c0 = 1; c0 < call.ctas_per_rank; c0 += 8) {
+            uint64_t w[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (c0 + u < call.ctas_per_rank) w[u] = ld_relaxed_sys_u64(rk.hist_parts + static_cast<int64_t>(c0 + u) * Lpad + i);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (c0 + u < call.ctas_per_rank) {
+                    if (static_cast<uint32_t>(w[u] >> 32) != tag &&
+                        !wait_tagged_word(rk.hist_parts + static_cast<int64_t>(c0 + u) * Lpad + i, tag,
+                                          *reinterpret_cast<volatile int*>(&s_timeout_peer) >= 0 ? 0 : call.timeout_ns, w[u])) {
+                        atomicMax(&s_timeout_peer, rk.my_rank);
+                        w[u] = 0;
+                    }
+                    total += static_cast<int32_t>(static_cast<uint32_t>(w[u]));
+                }
+            }
+        }
+        hist[i] = total;
+    }
     __syncthreads();
+    if (tid == 0) *rk.epochs = epoch;  // every CTA of the launch has read the old value: its partial carried the tag
+    if (s_timeout_peer >= 0) {  // a CTA of this very launch never delivered
+        if (tid == 0) report_error(rk.status, UEP_DEV_TIMEOUT_GATHER, s_timeout_peer);
+        return;
+    }
+    stamp(0);
+
+    // 2. publish the row to every rank (itself included). Every 64-bit word carries the epoch beside its
+    //    count, so a row needs neither a fence nor a flag: one NVLink crossing, and the reader knows a word
+    //    is this layer's when it sees it.
+    const int slot = static_cast<int>(epoch & 1ull);
+    const int me = rk.my_rank;
     if (me != call.withhold_rank) {
         for (int idx = tid; idx < N * L; idx += blockDim.x) {
             const int p = idx / L, i = idx % L;
@@ -344,10 +364,10 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int plan_ctas_per_rank(int input_kind, int max_T, int K_or_L, int nlocal, int num_sms) {
     const int64_t bytes = static_cast<int64_t>(max_T) * K_or_L * (input_kind == 0 ? 1 : (input_kind == 1 ? 4 : 8));
     int ctas = static_cast<int>((bytes + 16 * 1024 - 1) / (16 * 1024));
-    const int cap = nlocal > 1 ? (num_sms / nlocal) : 32;
+    const int cap = nlocal > 1 ? (num_sms / nlocal) : kPlanMaxCtas;
     ctas = ctas < 1 ? 1 : ctas;
     ctas = ctas > cap ? cap : ctas;
-    return ctas > 32 ? 32 : (ctas < 1 ? 1 : ctas);
+    return ctas > kPlanMaxCtas ? kPlanMaxCtas : (ctas < 1 ? 1 : ctas);
 }
 
 cudaError_t launch_plan(const PlanCall& call, cudaStream_t stream) {
