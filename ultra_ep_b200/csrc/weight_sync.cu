@@ -23,8 +23,9 @@
 // Relay (optional; the reference's relay plan, csrc/kernels/weight_sync.cu:129-191, 295-502,
 // exists only for NVLink domains above 8 ranks and raises one ready flag per chunk of tiles,
 // :638-677). A relayed expert with r replicas is broadcast as scatter + forward in chunks of
-// four tiles (128 KiB): its master sends chunk c only to replica c mod r and raises that chunk's
-// ready flag there once the chunk's stores are complete (one system-scope fence per chunk);
+// four tiles (128 KiB; one-tile chunks with a flag each measured slower): its master sends chunk
+// c only to replica c mod r and raises that chunk's ready flag there once the chunk's stores are
+// complete (a system-scope fence in a thread of its own, one fence for all flags that are due);
 // every replica forwards the chunks it received from the master to the other r-1 replicas. The
 // master's rank then sends the expert once instead of r times, and the forwarding load is
 // spread over the replicas' ranks. Which experts are relayed is a pure function of the plan and
@@ -53,6 +54,10 @@ constexpr int kMaxFwd = 64;                       // replica slots of the hosted
 constexpr int kMaxRelayReplicas = 16;
 constexpr int kMaxFwdDst = kMaxFwd * (kMaxRelayReplicas - 1);
 constexpr int kChunkTiles = 4;                    // tiles per relayed chunk (one ready flag per chunk)
+// A relayed chunk's flag is raised once the store group kFlagDepth groups behind the newest one is complete.
+// A CTA moves about 32 KiB per NVLink round trip when 64 of them share the link, so every group of depth
+// delays the second hop by about 3 us; the issuing thread waits at a chunk's end only.
+constexpr int kFlagDepth = 1;
 
 // One unit of work as the counter hands it out.
 struct Unit {
@@ -712,14 +717,15 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                         }
                         bulk_commit();
                         // A chunk's ready flag may go out once its stores are complete, not merely read: the flag
-                        // owed for the tile stored kSyncStages-1 iterations ago is due now (groups complete in order,
+                        // owed for the tile stored kFlagDepth iterations ago is due now (groups complete in order,
                         // so the earlier tiles of that chunk are complete as well).
                         if (kR) {
-                            uint64_t* due = owed[(k + 1) % kSyncStages];
-                            owed[(k + 1) % kSyncStages] = nullptr;
+                            const int ds = (k + kSyncStages - kFlagDepth) % kSyncStages;
+                            uint64_t* due = owed[ds];
+                            owed[ds] = nullptr;
                             owed[s] = ring_flag[s];
                             if (due != nullptr) {
-                                bulk_wait_all<kSyncStages - 1>();
+                                bulk_wait_all<kFlagDepth>();
                                 post_flag(due);
                             }
                         }
@@ -760,11 +766,12 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                 while (true) {
                     const int head = sm.post_head;
                     if (tail < head) {
+                        // one fence for every flag handed over so far: a system-scope fence takes about a link
+                        // round trip while the CTA's stores are in flight, the flags queue up behind it
                         __threadfence_block();
-                        uint64_t* flag = sm.post[tail & 7];
-                        __threadfence_system();  // the chunk's stores, seen complete by the issuing thread, before the flag
-                        st_relaxed_sys_u64(flag, epoch);
-                        sm.post_tail = ++tail;
+                        __threadfence_system();  // the chunks' stores, seen complete by the issuing thread, before the flags
+                        for (; tail < head; ++tail) st_relaxed_sys_u64(sm.post[tail & 7], epoch);
+                        sm.post_tail = tail;
                     } else if (sm.post_done && tail >= sm.post_head) {
                         break;
                     } else {
