@@ -1395,6 +1395,62 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------
 # small fixed cases of single kernels, for profiler captures (a few hundred MB on the device, a handful of launches)
 # ------------------------------------------------------------------------------------------
+def run_device_trace(args):
+    """Device-side time stamps of weight_sync (and of the plan kernel in front of it) at full size, one rank per GPU or
+    EP8 simulated: per rank and launch the CUDA-event time and the kernel's own stamps (set-up done, last copy issued,
+    last copy complete, ticket, end). The stamps are a tuning aid of the library (UEP_SYNC_TRACE=1)."""
+    os.environ["UEP_SYNC_TRACE"] = "1"
+    import ctypes as C  # noqa: F401
+
+    from ultra_ep_b200 import capi
+    from ultra_ep_b200 import workloads as W
+
+    env = Env()
+    torch = env.torch
+    args.plan_mode_resolved = args.plan_mode if args.plan_mode >= 0 else (0 if env.world == 1 else 1)
+    base = W.CONFIGS[args.config]
+    cfg = base.with_ep(env.world) if env.world > 1 else base
+    fw = Forward(env, cfg, args, 2, 10)
+    g, t = fw.group, fw.masters.tables
+    comm = g.comm_stream()
+    rows = []
+    for mb in range(10):
+        ids = fw.ids_dev[mb]
+        for rep in range(2):  # the second launch of a microbatch is the one reported
+            env.barrier()
+            with torch.cuda.stream(comm):
+                env.flush_l2()
+                g.update_placement(0, ids)
+                a, b = timed(torch, lambda: g.weight_sync(0, t[0], t[1], t[2], t[3]), stream=comm)
+            env.barrier()
+        buf = np.zeros((1024, 8), np.uint64)
+        capi.check(g.lib.uep_debug_sync_trace(g.handle, buf.ctypes.data, 1024))
+        st = buf[:512]
+        st = st[st[:, 0] > 0].astype(np.int64)
+        t0 = st[:, 0].min()
+        rel = (st - t0) / 1e3
+        vol = fw.volumes(0)
+        pl = buf[1000].astype(np.int64)
+        rows.append({"microbatch": mb, "rank": env.rank, "event_us": round(a.elapsed_time(b) * 1e3, 1),
+                     "egress_experts": [round(float(v["egress"]), 2) for v in vol], "ingress_experts": [v["ingress"] for v in vol],
+                     "ctas": int(len(st)), "setup_us": round(float(np.median(rel[:, 1])), 1),
+                     "last_copy_complete_us": round(float(rel[:, 3].max()), 1), "last_ticket_us": round(float(rel[:, 5].max()), 1),
+                     "end_us": round(float(rel[:, 6].max()), 1),
+                     "plan_kernel_us": {"partials": round((pl[0] - pl[5]) / 1e3, 1), "published": round((pl[1] - pl[5]) / 1e3, 1),
+                                        "gathered": round((pl[2] - pl[5]) / 1e3, 1), "solved": round((pl[4] - pl[5]) / 1e3, 1)}})
+    g.check_status()
+    if env.world > 1:
+        allrows = [None] * env.world
+        env.dist.all_gather_object(allrows, rows)
+    else:
+        allrows = [rows]
+    if env.rank == 0:
+        for mb in range(10):
+            for r in range(len(allrows)):
+                print(json.dumps(allrows[r][mb]))
+    fw.close()
+
+
 def run_profile_case(args):
     import ctypes as C
 
@@ -1651,11 +1707,14 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip cfg 1, 2, 5 and the EP64 replay")
     ap.add_argument("--no-manager", action="store_true", help="skip the Manager-API section (N > 1)")
     ap.add_argument("--reduce-sms", type=int, default=42, help="CTAs of the Wgrad reduce kernel (reference default 42)")
-    ap.add_argument("--profile-case", default="", choices=["", "dense", "sparse", "gather", "reduce", "plan", "sync"],
-                    help="run six launches of one kernel family on a small fixed case and exit (for profiler captures)")
+    ap.add_argument("--profile-case", default="", choices=["", "dense", "sparse", "gather", "reduce", "plan", "sync", "trace"],
+                    help="run six launches of one kernel family on a small fixed case and exit (for profiler captures); "
+                         "trace: print the device-side time stamps of weight_sync at full size, at any N, and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.profile_case == "trace":
+        run_device_trace(args)
     elif args.profile_case:
         run_profile_case(args)
     else:
