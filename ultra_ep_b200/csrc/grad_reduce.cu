@@ -10,8 +10,9 @@
 // with per-thread stores, repeat). Here:
 //   * no task list: every CTA derives the pull list from the plan rows with a block scan;
 //   * a consumed replica region is not zeroed over the link. Pulling 75 MB and pushing 75 MB of
-//     zeros back at the same time measured 450 GB/s against 660 GB/s for the pull alone: the two
-//     directions of a GPU's NVLink port do not add up. Instead the rank that HOSTS a replica
+//     zeros back at the same time measured 450 GB/s against 660 GB/s for the pull alone (the link
+//     is full duplex, but one kernel reading from a peer and writing to it through the same SMs
+//     did not get both directions at full rate). Instead the rank that HOSTS a replica
 //     zeroes it in its own memory: the master's launch reports its progress in 16 segments
 //     (a counter per segment that every CTA bumps when it has consumed its items of the segment;
 //     the CTA that completes a segment stores "epoch, segments done" into a flag word on every
