@@ -1587,6 +1587,11 @@ def run_ours(args):
         with torch.cuda.graph(graph):
             fw.step(0, fw.ids_stage)
         env.barrier()
+        for i in range(3):  # untimed: the first replay uploads the instantiated graph to the device
+            fw.stage_all.copy_(fw.ids_all_dev[i % pool], non_blocking=True)
+            env.flush_l2()
+            graph.replay()
+        env.barrier()
         evs = []
         for i in range(args.steps):
             fw.stage_all.copy_(fw.ids_all_dev[i % pool], non_blocking=True)
