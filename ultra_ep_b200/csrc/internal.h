@@ -38,7 +38,7 @@ struct RankDev {
     uint64_t* peer_reduce_flags[kMaxPeers]; // each: [N], entry [src] = epoch * 64 + segments of its pulls master rank src has finished
     int* reduce_counters;    // [kReduceSegments]: CTAs of the running Wgrad reduce that have passed each segment; zero between calls
     DeviceStatus* status;    // mapped pinned host memory
-    // [0] plan epoch, [1] sync epoch, [2] Wgrad-reduce epoch: counted on the device (by the CTA that finishes a launch), not
+    // [0] plan epoch, [1] sync epoch, [2] Wgrad-reduce epoch: counted on the device (by one CTA of every launch), not
     // passed by value, so that a captured CUDA graph can be replayed: every replay is a new epoch
     uint64_t* epochs;
 };
