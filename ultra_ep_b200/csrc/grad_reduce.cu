@@ -276,11 +276,17 @@ __global__ void __launch_bounds__(kReduceThreads, 1) grad_reduce_kernel(ReduceCa
         // ---- reporting warp: keeps the atomics and the flag stores of the progress report off the threads that
         //      feed the rings (each costs a round trip to memory) -----------------------------------------------
         if (tid == kReduceConsumers + 96) {
+            // waits for threads of its own CTA only, whose waits are all bounded; bounded itself all the same
+            const uint64_t t_begin = global_timer_ns();
             while (true) {
                 const int fin = sm.pull_finished;
                 const long long done = fin ? static_cast<long long>(count) : sm.done_items;
                 report_progress(done);
                 if (fin || seg_next >= kReduceSegments) break;
+                if (global_timer_ns() - t_begin > 4 * call.timeout_ns) {
+                    report_error(status0, UEP_DEV_TIMEOUT_COPY, blockIdx.x);
+                    break;
+                }
                 __nanosleep(200);
             }
             report_progress(count);  // whatever happened, the counter of every segment sees this CTA exactly once

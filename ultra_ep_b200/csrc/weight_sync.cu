@@ -606,7 +606,16 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                 int posted = 0;
                 // hands a ready flag whose chunk is complete to the posting thread (which fences and stores it)
                 auto post_flag = [&](uint64_t* flag) {
-                    while (posted - sm.post_tail >= 8) __nanosleep(50);
+                    // the posting thread never blocks; bounded all the same (a flag that is dropped here shows up
+                    // as a time-out of the rank that waits for it)
+                    const uint64_t t_begin = global_timer_ns();
+                    while (posted - sm.post_tail >= 8) {
+                        if (global_timer_ns() - t_begin > call.timeout_ns) {
+                            report_error(status0, UEP_DEV_TIMEOUT_COPY, -1);
+                            return;
+                        }
+                        __nanosleep(50);
+                    }
                     sm.post[posted & 7] = flag;
                     __threadfence_block();
                     sm.post_head = ++posted;
@@ -763,9 +772,12 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
             } else if (kR && tid == 32) {
                 // ---- posting thread: raises the ready flags the issuing thread hands over ------------------
                 int tail = 0;
+                uint64_t t_idle = global_timer_ns();  // since the last flag: the issuing thread's own waits are bounded,
+                                                      // so is this one
                 while (true) {
                     const int head = sm.post_head;
                     if (tail < head) {
+                        t_idle = global_timer_ns();
                         // one fence for every flag handed over so far: a system-scope fence takes about a link
                         // round trip while the CTA's stores are in flight, the flags queue up behind it
                         __threadfence_block();
@@ -775,6 +787,7 @@ __global__ void __launch_bounds__(kSyncThreads) weight_sync_kernel(SyncCall call
                     } else if (sm.post_done && tail >= sm.post_head) {
                         break;
                     } else {
+                        if (global_timer_ns() - t_idle > 8 * call.timeout_ns) break;
                         __nanosleep(100);
                     }
                 }
