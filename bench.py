@@ -17,7 +17,9 @@ slots per rank, fp8 weights with UE8M0 scales).
 
 Prints ONE JSON line (rank 0):
   value         microseconds per layer, inputs resident on the device, C-ABI calls (mean over the timed
-                steps of the per-step maximum over ranks; `step_stats` adds median and percentiles)
+                steps of the per-step maximum over ranks; `step_stats_us` adds median and percentiles,
+                `value_statistic` the largest of the ranks' own means). At N > 1 the ranks are lined up on the
+                device (a one-word all-reduce on the stream) in front of every L2 flush, outside the timed events
   e2e           the same step driven from pinned host buffers (routing ids copied in, physical ids
                 copied out, every step): through the drop-in `Manager` (pybind module `_C`) at N > 1,
                 through the C ABI on the simulated group at N = 1 (the Manager hosts one rank per process)
@@ -30,6 +32,9 @@ Prints ONE JSON line (rank 0):
   backward      cfg 4: Wgrad reduce, token-gradient gather, dense reroute forward/backward
   configs       cfg 1, cfg 2 and cfg 5 (forward + backward with four microbatch slots in flight)
   cpu_baseline  the CPU oracle timed on a bounded sample of the same workload (N = 1)
+
+--profile-case NAME runs a few launches of one kernel family and exits (for profiler captures); NAME = trace prints
+the kernels' own time stamps of plan and weight_sync at full size, at any N.
 
 --impl reference times the reference's logic for this path on the host cores (the CPU
 restatement under oracle/: the reference itself has no CPU implementation of this path).
